@@ -21,6 +21,7 @@ class CacheInstance:
     group: int
     num_kv_heads: int
     head_dim: int
+    values: bool = True       # False: keys and values are the same vectors; only one tensor of pages is kept
 
 
 def element_size(dtype: torch.dtype) -> int:
@@ -29,7 +30,7 @@ def element_size(dtype: torch.dtype) -> int:
 
 def bytes_per_page(instances: List[CacheInstance], group: int, page_size: int, dtype: torch.dtype) -> int:
     """Bytes that one more page of this group costs over all its instances (K and V)."""
-    return sum(2 * page_size * i.num_kv_heads * i.head_dim * element_size(dtype)
+    return sum((2 if i.values else 1) * page_size * i.num_kv_heads * i.head_dim * element_size(dtype)
                for i in instances if i.group == group)
 
 
@@ -45,13 +46,15 @@ class CacheStorage:
         for inst in instances:
             shape = (pages_per_group[inst.group], inst.num_kv_heads, page_size, inst.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            # an instance without values hands out its key pages as value pages too
+            self.v.append(torch.zeros(shape, dtype=dtype, device=device) if inst.values else self.k[-1])
 
     def pages(self, instance: int) -> Tuple[torch.Tensor, torch.Tensor]:
         return self.k[instance], self.v[instance]
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.k + self.v)
+        distinct = {t.data_ptr(): t for t in self.k + self.v}
+        return sum(t.numel() * t.element_size() for t in distinct.values())
 
     def poison(self, group: int, pages: List[int]) -> None:
         """Debug aid: fill these pages of every instance of the group with POISON, so that a kernel
@@ -65,7 +68,8 @@ class CacheStorage:
         for inst, k, v in zip(self.instances, self.k, self.v):
             if inst.group == group:
                 k.index_fill_(0, idx, POISON)
-                v.index_fill_(0, idx, POISON)
+                if v is not k:
+                    v.index_fill_(0, idx, POISON)
 
 
 class StateStorage:

@@ -134,6 +134,87 @@ class LlamaConfig:
 
 
 @dataclass(frozen=True)
+class TevudraConfig:
+    """config.json of a Tevudra folder: a decoder whose layers are listed one by one.
+
+    Top level: `architecture`, `width`, `vocab`, `norm.eps`, `layers`.  A layer gives `type` (its
+    mixer), `mixer` (the mixer's sizes and constants) and `mlp` (its feed-forward, or null).
+    latent_attention mixer: heads, dim, vdim, kv_rank, scale, and kv_from (the layer whose latents
+    it reads) where it keeps none of its own.  mlp: {kind: dense, ff} or {kind: moe, expert: {ff},
+    router: {experts, top}, shared: {ff} or absent}.  The design has no positions, so no length
+    limit of its own: max_position (optional) bounds what the engine sizes its tables for."""
+
+    architecture: str
+    width: int
+    vocab: int
+    norm_eps: float
+    layers: tuple                      # of dicts, validated
+    max_position: int = 131072
+    eos_token_id: Optional[int] = None
+
+    MIXERS = ("latent_attention",)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "TevudraConfig":
+        norm = _take(d, "norm", dict)
+        layers = _take(d, "layers", list)
+        if not layers:
+            raise ConfigError("config.json: 'layers' must list at least one layer")
+        out = []
+        for i, layer in enumerate(layers):
+            where = f"layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"config.json: {where} must be an object")
+            kind = _take(layer, "type", str)
+            if kind not in cls.MIXERS:
+                raise ConfigError(f"config.json: {where}.type '{kind}' is not a mixer of this design {cls.MIXERS}")
+            m = _take(layer, "mixer", dict)
+            mixer = {k: _take(m, k, int) for k in ("heads", "dim", "vdim", "kv_rank")}
+            mixer["scale"] = _take(m, "scale", float)
+            mixer["kv_from"] = _take(m, "kv_from", int, None)
+            if min(mixer[k] for k in ("heads", "dim", "vdim", "kv_rank")) <= 0:
+                raise ConfigError(f"config.json: {where}.mixer sizes must be positive")
+            src = mixer["kv_from"]
+            if src is not None:
+                if not (0 <= src < i) or out[src]["mixer"]["kv_from"] is not None:
+                    raise ConfigError(f"config.json: {where}.mixer.kv_from={src} must name an earlier layer that keeps its own latents")
+                if out[src]["mixer"]["kv_rank"] != mixer["kv_rank"]:
+                    raise ConfigError(f"config.json: {where}.mixer.kv_rank differs from that of layer {src}, whose latents it reads")
+            ff = layer.get("mlp")
+            mlp = None
+            if ff is not None:
+                if not isinstance(ff, dict):
+                    raise ConfigError(f"config.json: {where}.mlp must be an object or null")
+                fk = _take(ff, "kind", str)
+                if fk == "dense":
+                    mlp = {"kind": "dense", "ff": _take(ff, "ff", int)}
+                elif fk == "moe":
+                    router = _take(ff, "router", dict)
+                    shared = ff.get("shared")
+                    mlp = {"kind": "moe", "ff": _take(_take(ff, "expert", dict), "ff", int),
+                           "experts": _take(router, "experts", int), "top": _take(router, "top", int),
+                           "shared_ff": _take(shared, "ff", int) if isinstance(shared, dict) else 0}
+                    if not (0 < mlp["top"] <= mlp["experts"]):
+                        raise ConfigError(f"config.json: {where}.mlp.router: top {mlp['top']} of {mlp['experts']} experts")
+                else:
+                    raise ConfigError(f"config.json: {where}.mlp.kind '{fk}' is not 'dense' or 'moe'")
+                if mlp["ff"] <= 0:
+                    raise ConfigError(f"config.json: {where}.mlp: ff must be positive")
+            out.append({"type": kind, "mixer": mixer, "mlp": mlp})
+        eos = d.get("eos_token_id")
+        cfg = cls(architecture=_take(d, "architecture", str), width=_take(d, "width", int), vocab=_take(d, "vocab", int),
+                  norm_eps=_take(norm, "eps", float), layers=tuple(out),
+                  max_position=_take(d, "max_position", int, 131072), eos_token_id=eos if isinstance(eos, int) else None)
+        if cfg.width <= 0 or cfg.vocab <= 0 or cfg.max_position <= 0:
+            raise ConfigError("config.json: width, vocab and max_position must be positive")
+        return cfg
+
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_position
+
+
+@dataclass(frozen=True)
 class Architecture:
     """One registry entry: how to read the config and how to lay the model out."""
 
@@ -168,10 +249,13 @@ def _ensure_builtin() -> None:
 
 
 def parse_config(d: Dict[str, Any]):
-    """config.json contents -> (Architecture, typed config)."""
+    """config.json contents -> (Architecture, typed config).  The architecture is the first name of
+    the list `architectures`, or the string `architecture`."""
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]
     if not isinstance(archs, list) or not archs:
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' a name)")
     arch = get_architecture(archs[0])
     return arch, arch.config_class.from_dict(d)
 

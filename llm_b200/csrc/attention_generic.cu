@@ -15,7 +15,7 @@
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_HEAD_DIM = 256;
+constexpr int MAX_HEAD_DIM = 512;      // the kernel is built for head sizes up to 256 and up to 512
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int head_dim);
@@ -59,7 +59,7 @@ __device__ __forceinline__ float dot_row_scalar(const float* __restrict__ q, con
   return s;
 }
 
-template <typename T>
+template <typename T, int MAXD>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ q,
                                long long q_stride, const T* __restrict__ k_pages,
@@ -67,7 +67,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
                                int table_width, const int* __restrict__ token_entry,
                                const int* __restrict__ positions, int n_tokens, int n_heads, int n_kv,
                                int head_dim, int page_size, int window, float scale, bool vec) {
-  __shared__ float q_s[WARPS][MAX_HEAD_DIM];
+  __shared__ float q_s[WARPS][MAXD];
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -83,9 +83,9 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
   for (int d = lane; d < head_dim; d += 32) q_s[warp][d] = to_f32(q_row[d]);
   __syncwarp();
 
-  float acc[MAX_HEAD_DIM / 32];
+  float acc[MAXD / 32];
 #pragma unroll
-  for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
+  for (int i = 0; i < MAXD / 32; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
 
   for (int tile = (lo / 32) * 32; tile <= pos; tile += 32) {
@@ -104,7 +104,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
     l = l * alpha + warp_sum(p);
     m = m_new;
 #pragma unroll
-    for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[i] *= alpha;
+    for (int i = 0; i < MAXD / 32; ++i) acc[i] *= alpha;
     const int n_valid = min(32, pos - tile + 1);
     for (int j = 0; j < n_valid; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
@@ -112,7 +112,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
       if (pj != 0.f) {
         const T* v = v_pages + rj;
 #pragma unroll
-        for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
+        for (int i = 0; i < MAXD / 32; ++i) {
           const int d = lane + 32 * i;
           if (d < head_dim) acc[i] = fmaf(pj, to_f32(v[d]), acc[i]);
         }
@@ -122,7 +122,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
   const float inv = 1.f / l;
   T* o = out + (size_t)t * out_stride + (size_t)h * head_dim;
 #pragma unroll
-  for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
+  for (int i = 0; i < MAXD / 32; ++i) {
     const int d = lane + 32 * i;
     if (d < head_dim) o[d] = from_f32<T>(acc[i] * inv);
   }
@@ -149,9 +149,14 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     const bool vec = head_dim % (16 / (int)sizeof(T)) == 0 && (uintptr_t)k_pages % 16 == 0;      // whole 16-byte pieces per key row
-    launch_kernel(paged_attention_generic_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
-        (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
-        table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
+    if (head_dim <= 256)
+      launch_kernel(paged_attention_generic_kernel<T, 256>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
+          (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
+          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
+    else      // the wide head of a latent attention (its rank)
+      launch_kernel(paged_attention_generic_kernel<T, MAX_HEAD_DIM>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
+          (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
+          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
     LLMK_LAUNCH_CHECK("paged_attention_generic");
   });
 }

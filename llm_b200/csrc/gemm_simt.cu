@@ -35,13 +35,18 @@ __device__ __forceinline__ void load_k(const T* __restrict__ row, int k, int K, 
 template <typename T, typename TC, int VEC>
 __global__ void __launch_bounds__(THREADS)
 gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
-                 long long lda, long long ldw, long long ldc) {
+                 long long lda, long long ldw, long long ldc, long long a_batch, long long w_batch, long long c_batch,
+                 const T* __restrict__ gate, long long gate_stride) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  // blockIdx.z: one of several products of the same sizes (the heads of a per-head projection)
+  A += (size_t)blockIdx.z * a_batch;
+  W += (size_t)blockIdx.z * w_batch;
+  C += (size_t)blockIdx.z * c_batch;
   const int lrow = tid >> 2, lk = (tid & 3) * 4;
   const int ty = tid >> 4, tx = tid & 15;
   const bool a_ok = m0 + lrow < M, w_ok = n0 + lrow < N;
@@ -81,24 +86,29 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, TC* __restric
   for (int i = 0; i < TM; ++i) {
     const int m = m0 + ty * TM + i;
     if (m >= M) continue;
+    // a gate per (row, product): the row's results are multiplied by sigmoid(gate[m, z])
+    const float g = gate ? 1.f / (1.f + expf(-to_f32(gate[(size_t)m * gate_stride + blockIdx.z]))) : 1.f;
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
-      if (n < N) C[(size_t)m * ldc + n] = from_f32<TC>(acc[i][j]);
+      if (n < N) C[(size_t)m * ldc + n] = from_f32<TC>(gate ? acc[i][j] * g : acc[i][j]);
     }
   }
 }
 
 template <typename T, typename TC>
 int launch(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
-           long long ldc, cudaStream_t stream) {
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) &&
+           long long ldc, cudaStream_t stream, int batches = 1, long long a_batch = 0, long long w_batch = 0,
+           long long c_batch = 0, const void* gate = nullptr, long long gate_stride = 0) {
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batches);
+  const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) && (a_batch % 4 == 0) && (w_batch % 4 == 0) &&
                    ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
   if (vec)
-    launch_kernel(gemm_simt_kernel<T, TC, 4>, grid, dim3(THREADS), 0, stream, (const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+    launch_kernel(gemm_simt_kernel<T, TC, 4>, grid, dim3(THREADS), 0, stream, (const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc,
+                  a_batch, w_batch, c_batch, (const T*)gate, gate_stride);
   else
-    launch_kernel(gemm_simt_kernel<T, TC, 1>, grid, dim3(THREADS), 0, stream, (const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+    launch_kernel(gemm_simt_kernel<T, TC, 1>, grid, dim3(THREADS), 0, stream, (const T*)A, (const T*)W, (TC*)C, M, N, K, lda, ldw, ldc,
+                  a_batch, w_batch, c_batch, (const T*)gate, gate_stride);
   LLMK_LAUNCH_CHECK("gemm_simt");
 }
 
@@ -116,4 +126,21 @@ LLMK_API int llmk_gemm_simt(const void* A, const void* W, void* C, int M, int N,
   if (in_dtype == LLMK_BF16 && out_dtype == LLMK_F32)
     return launch<__nv_bfloat16, float>(A, W, C, M, N, K, lda, ldw, ldc, stream);
   return llmk_fail(-1, "gemm_simt: unsupported element kinds in=%d out=%d", in_dtype, out_dtype);
+}
+
+// `batches` products of the same sizes in one launch: product z reads A + z * a_batch, W + z * w_batch
+// and writes C + z * c_batch (strides in elements).  With a gate ([M, gate_stride] of the input kind),
+// row m of product z is multiplied by sigmoid(gate[m, z]).  The per-head projections of a latent
+// attention are such a batch: the columns of one head in, the columns of one head out.
+LLMK_API int llmk_gemm_simt_batched(const void* A, const void* W, void* C, int M, int N, int K, long long lda,
+                                    long long ldw, long long ldc, int batches, long long a_batch, long long w_batch,
+                                    long long c_batch, const void* gate, long long gate_stride, int dtype,
+                                    cudaStream_t stream) {
+  if (M == 0 || N == 0 || batches == 0) return 0;
+  LLMK_REQUIRE(K > 0 && lda >= K && ldw >= K && ldc >= N, "gemm_simt_batched: bad sizes M=%d N=%d K=%d", M, N, K);
+  LLMK_REQUIRE((M + BM - 1) / BM <= 65535 && batches <= 65535, "gemm_simt_batched: M=%d or %d batches exceed the grid limit", M, batches);
+  if (dtype == LLMK_F32) return launch<float, float>(A, W, C, M, N, K, lda, ldw, ldc, stream, batches, a_batch, w_batch, c_batch, gate, gate_stride);
+  if (dtype == LLMK_BF16)
+    return launch<__nv_bfloat16, __nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, stream, batches, a_batch, w_batch, c_batch, gate, gate_stride);
+  return llmk_fail(-1, "gemm_simt_batched: unsupported element kind %d", dtype);
 }

@@ -135,6 +135,127 @@ def add_rmsnorm(resid: torch.Tensor, delta, gamma: torch.Tensor, out, rows: int,
                                    c_int(hidden), c_float(eps), c_int(_kind(ref.dtype)), _stream()))
 
 
+def add_dyt(resid: torch.Tensor, delta, w: torch.Tensor, b: torch.Tensor, alpha: float, out, rows: int) -> None:
+    """resid[:rows] += delta (a tensor or a PartialSum, if given); out[:rows] = tanh(alpha * resid) * w + b
+    (if out given): Dynamic Tanh, a norm without statistics."""
+    assert resid.dtype == torch.float32 and w.dtype == torch.float32 and b.dtype == torch.float32
+    assert resid.is_contiguous() and w.is_contiguous() and b.is_contiguous()
+    hidden = resid.shape[-1]
+    ref = out if out is not None else delta
+    if ref is None:
+        return
+    if isinstance(delta, PartialSum):
+        assert delta.cols == hidden and delta.rows == rows
+    elif delta is not None:
+        assert delta.is_contiguous() and delta.shape[-1] == hidden
+    if out is not None:
+        assert out.is_contiguous() and out.shape[-1] == hidden
+        if delta is not None:
+            assert delta.dtype == out.dtype
+    d, parts, splits, stride = _split_args(delta)
+    _check(load().llmk_add_dyt(_ptr(resid), d, parts, splits, stride, _ptr(w), _ptr(b), c_float(alpha), _ptr(out),
+                               c_int(rows), c_int(hidden), c_int(_kind(ref.dtype)), _stream()))
+
+
+ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def act_rows(out: torch.Tensor, x, rows: int, kind: str) -> None:
+    """out[:rows] = act(x[:rows]) element by element in float32; x a tensor or a PartialSum.
+    kind: "relu2" (the square of relu), "gelu" (erf), "gelu_tanh", "silu"."""
+    cols = out.shape[-1]
+    assert out.is_contiguous() and out.dtype == x.dtype
+    if isinstance(x, PartialSum):
+        assert x.cols == cols and x.rows == rows
+    else:
+        assert x.is_contiguous() and x.shape[-1] == cols
+    d, parts, splits, stride = _split_args(x)
+    _check(load().llmk_act_rows(_ptr(out), d, parts, splits, stride, c_longlong(rows * cols), c_int(ACTIVATIONS[kind]),
+                                c_int(_kind(out.dtype)), _stream()))
+
+
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, heads: int, gate=None) -> None:
+    """Per-head products in one launch: out[:, h*N:(h+1)*N] = a[:, h*K:(h+1)*K] @ w[h].T for w [heads, N, K];
+    with a gate [rows, >= heads] (a view with unit column stride) head h of a row is multiplied by
+    sigmoid(gate[row, h]).  Float32 accumulation on the CUDA cores in a fixed k order."""
+    _rows_contig(a, "a"); _rows_contig(out, "out")
+    assert w.dim() == 3 and w.is_contiguous() and w.shape[0] == heads and a.dtype == w.dtype == out.dtype
+    n, k = w.shape[1], w.shape[2]
+    assert a.shape[1] == heads * k and out.shape[1] == heads * n
+    if gate is not None:
+        _rows_contig(gate, "gate")
+        assert gate.dtype == a.dtype and gate.shape[1] >= heads
+    _check(load().llmk_gemm_simt_batched(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
+                                         c_longlong(a.stride(0)), c_longlong(k), c_longlong(out.stride(0)), c_int(heads),
+                                         c_longlong(k), c_longlong(n * k), c_longlong(n), _ptr(gate),
+                                         c_longlong(gate.stride(0) if gate is not None else 0), c_int(_kind(a.dtype)), _stream()))
+
+
+def latent_norm_store(x: torch.Tensor, gain: torch.Tensor, eps: float, slot_map: torch.Tensor, pages: torch.Tensor,
+                      n_tokens: int) -> None:
+    """pages[slot_map[t]] = x[t] / sqrt(mean(x[t]^2) + eps) * gain for the first rank columns of x;
+    pages [pages, 1, page_size, rank]."""
+    _rows_contig(x, "x")
+    rank = pages.shape[3]
+    assert pages.is_contiguous() and pages.shape[1] == 1 and pages.dtype == x.dtype and x.shape[1] >= rank
+    assert gain.dtype == torch.float32 and gain.numel() == rank and slot_map.dtype == torch.int32
+    _check(load().llmk_latent_norm_store(_ptr(x), c_longlong(x.stride(0)), _ptr(gain), c_float(eps), _ptr(slot_map),
+                                         _ptr(pages), c_int(n_tokens), c_int(rank), c_int(_kind(x.dtype)), _stream()))
+
+
+@functools.lru_cache(maxsize=None)
+def moe_tile() -> int:
+    """Slots per tile of the grouped products."""
+    return int(load().llmk_moe_tile())
+
+
+def moe_max_tiles(n_pairs: int, experts: int) -> int:
+    """Tiles that the grouped list of n_pairs (token, choice) pairs can take at most."""
+    return _ceil_div(n_pairs, moe_tile()) + min(experts, n_pairs)
+
+
+def moe_route(h: torch.Tensor, w: torch.Tensor, bias, ids: torch.Tensor, weights: torch.Tensor, n_tokens: int, top: int) -> None:
+    """Router: float32 logits h @ w.T + bias, the `top` largest per token (ids, falling) and the softmax
+    over those alone (weights)."""
+    _rows_contig(h, "h")
+    assert w.is_contiguous() and w.dtype == h.dtype and w.shape[1] == h.shape[1]
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == w.shape[0])
+    _check(load().llmk_moe_route(_ptr(h), c_longlong(h.stride(0)), _ptr(w), _ptr(bias), _ptr(ids), _ptr(weights),
+                                 c_int(n_tokens), c_int(h.shape[1]), c_int(w.shape[0]), c_int(top), c_int(_kind(h.dtype)), _stream()))
+
+
+def moe_group(ids: torch.Tensor, n_pairs: int, experts: int, meta: torch.Tensor, tile_expert: torch.Tensor,
+              slot_src: torch.Tensor, pair_slot: torch.Tensor, max_tiles: int) -> None:
+    """Sort the pairs by expert into tiles (see routed.cu); all int32 on the device."""
+    for t in (ids, meta, tile_expert, slot_src, pair_slot):
+        assert t.dtype == torch.int32 and t.is_contiguous()
+    assert tile_expert.numel() >= max_tiles and slot_src.numel() >= max_tiles * moe_tile() and pair_slot.numel() >= n_pairs
+    _check(load().llmk_moe_group(_ptr(ids), c_int(n_pairs), c_int(experts), _ptr(meta), _ptr(tile_expert), _ptr(slot_src),
+                                 _ptr(pair_slot), c_int(max_tiles), _stream()))
+
+
+def moe_gemm(a: torch.Tensor, gather_div: int, slot_src, tile_expert, meta, w: torch.Tensor, out: torch.Tensor,
+             max_tiles: int, act=None) -> None:
+    """out[slot] = act(a[row of slot] @ w[expert of the slot's tile].T) for w [experts, N, K]; gather_div > 0:
+    the row is the slot's pair // gather_div (its token), 0: the slot itself."""
+    _rows_contig(a, "a"); _rows_contig(out, "out")
+    assert w.dim() == 3 and w.is_contiguous() and w.dtype == a.dtype and a.shape[1] == w.shape[2] and out.shape[1] == w.shape[1]
+    assert out.shape[0] >= max_tiles * moe_tile()
+    _check(load().llmk_moe_gemm(_ptr(a), c_longlong(a.stride(0)), c_int(gather_div), _ptr(slot_src), _ptr(tile_expert),
+                                _ptr(meta), _ptr(w), c_longlong(w.shape[2]), c_longlong(w.shape[1] * w.shape[2]), _ptr(out),
+                                c_longlong(out.stride(0)), c_int(w.shape[1]), c_int(w.shape[2]), c_int(max_tiles),
+                                c_int(ACTIVATIONS[act] if act else -1), c_int(_kind(a.dtype)), c_int(_kind(out.dtype)), _stream()))
+
+
+def moe_combine(out: torch.Tensor, y: torch.Tensor, pair_slot, weights, shared, n_tokens: int, top: int) -> None:
+    """out[t] = shared[t] (a tensor, a PartialSum or None) + sum_j weights[t, j] * y[pair_slot[t, j]]."""
+    assert out.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous() and y.shape[1] == out.shape[1]
+    d, parts, splits, stride = _split_args(shared)
+    _check(load().llmk_moe_combine(_ptr(out), _ptr(y), _ptr(pair_slot), _ptr(weights), d, parts, splits, stride,
+                                   c_int(n_tokens), c_int(top), c_int(out.shape[1]), c_int(_kind(out.dtype)), _stream()))
+
+
 def gather_rows(out: torch.Tensor, resid: torch.Tensor, delta, rows: torch.Tensor, n_rows: int) -> None:
     """out[r] = resid[rows[r]] (+ delta[rows[r]], a tensor or a PartialSum), float32."""
     assert out.dtype == torch.float32 and resid.dtype == torch.float32 and rows.dtype == torch.int32
@@ -388,7 +509,7 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     split-key decode kernel when every entry brings one token and the tcgen05 kernel otherwise,
     where it takes the sizes; the general kernel for float32 and for all other sizes (head sizes
     off the 16-grid among them)."""
-    if ctx.decode_only and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0:
+    if ctx.decode_only and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256:
         max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
         if window:
             max_keys = min(max_keys, window)

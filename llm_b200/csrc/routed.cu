@@ -1,0 +1,276 @@
+// A routed feed-forward (mixture of experts): router, grouping of the tokens by expert, the
+// experts' two products over the groups, and the weighted sum.
+//
+//   route    z = h Wr^T + b in float32; the `top` largest z of a token (ties to the lower index);
+//            their weights are the softmax over those `top` values alone.
+//   group    every (token, choice) pair gets a slot in a list that is sorted by expert, each
+//            expert's run padded to whole tiles of 64 slots, so that a tile of the products below
+//            belongs to one expert.  The launch sizes depend on the numbers of tokens, choices and
+//            experts only: what a step's routing turns out to be is read on the device.
+//   products C[slot] = act(A[row of slot] . W[expert of the slot's tile]^T), float32 accumulation in a
+//            fixed k order per element, so a pair's result does not depend on its slot or on what
+//            else is in the batch.
+//   combine  out[t] = shared[t] + sum_j weight[t, j] * y[slot of (t, j)], summed in the order of j.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROUTE_WARPS = 4;
+constexpr int MAX_EXPERTS = 256;
+constexpr int TILE = 64;          // slots per tile of the grouped products
+
+__device__ __forceinline__ float act_of(float z, int kind) {
+  switch (kind) {
+    case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 1: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+    case 2: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    case 3: return z / (1.f + expf(-z));
+    default: return z;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ w, const float* __restrict__ bias,
+             int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int width, int experts, int top) {
+  __shared__ float z_s[ROUTE_WARPS][MAX_EXPERTS];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= n_tokens) return;
+  const T* row = h + (size_t)t * h_stride;
+  for (int e = 0; e < experts; ++e) {
+    const T* we = w + (size_t)e * width;
+    float s = 0.f;
+    for (int c = lane; c < width; c += 32) s = fmaf(to_f32(row[c]), to_f32(we[c]), s);
+    s = warp_sum(s);
+    if (lane == 0) z_s[warp][e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  float z_max = 0.f, denom = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z_s[warp][e];
+      if (v > best) { best = v; arg = e; }            // ascending e: the first of equal values stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ov > best || (ov == best && oa < arg)) { best = ov; arg = oa; }
+    }
+    if (j == 0) z_max = best;
+    const float p = expf(best - z_max);
+    denom += p;
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = arg < experts ? arg : -1;      // no finite logit left: the pair is dropped
+      weights[(size_t)t * top + j] = p;
+      if (arg < experts) z_s[warp][arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float inv = 1.f / denom;
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] *= inv;
+  }
+}
+
+// One block.  counts -> padded offsets -> slots.  meta[0] = tiles in use.
+__global__ void __launch_bounds__(1024)
+group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ meta, int* __restrict__ tile_expert,
+             int* __restrict__ slot_src, int* __restrict__ pair_slot, int max_tiles) {
+  __shared__ int count[MAX_EXPERTS], offset[MAX_EXPERTS], cursor[MAX_EXPERTS];
+  __shared__ int total_tiles;
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      offset[e] = tiles * TILE;
+      const int n = (count[e] + TILE - 1) / TILE;
+      for (int k = 0; k < n && tiles + k < max_tiles; ++k) tile_expert[tiles + k] = e;
+      tiles += n;
+    }
+    total_tiles = tiles < max_tiles ? tiles : max_tiles;
+    meta[0] = total_tiles;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < total_tiles * TILE; i += blockDim.x) slot_src[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < 0 || e >= experts) { pair_slot[i] = -1; continue; }
+    const int slot = offset[e] + atomicAdd(&cursor[e], 1);
+    slot_src[slot] = i;
+    pair_slot[i] = slot;
+  }
+}
+
+constexpr int BN = 64, BK = 16, TM = 4, TN = 4, THREADS = 256;
+
+// C[slot, :] = act(A[row(slot), :] . W[expert]^T) for the slots of tile blockIdx.y.
+// gather_div > 0: row(slot) = slot_src[slot] / gather_div (the token of the pair); 0: row(slot) = slot.
+template <typename T, typename TC>
+__global__ void __launch_bounds__(THREADS)
+grouped_gemm_kernel(const T* __restrict__ A, long long lda, int gather_div, const int* __restrict__ slot_src,
+                    const int* __restrict__ tile_expert, const int* __restrict__ meta, const T* __restrict__ W,
+                    long long ldw, long long w_expert, TC* __restrict__ C, long long ldc, int N, int K, int act) {
+  __shared__ float As[BK][TILE + 4];
+  __shared__ float Ws[BK][BN + 4];
+  __shared__ int src_s[TILE];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * BN;
+  const T* We = W + (size_t)tile_expert[tile] * w_expert;
+  if (tid < TILE) src_s[tid] = slot_src[tile * TILE + tid];
+  __syncthreads();
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;
+  const int ty = tid >> 4, tx = tid & 15;
+  const int src = src_s[lrow];
+  const bool a_ok = src >= 0, w_ok = n0 + lrow < N;
+  const T* a_row = A + (size_t)(a_ok ? (gather_div > 0 ? src / gather_div : tile * TILE + lrow) : 0) * lda;
+  const T* w_row = We + (size_t)(w_ok ? n0 + lrow : 0) * ldw;
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    float av[4], wv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + lk + i;
+      av[i] = (a_ok && k < K) ? to_f32(a_row[k]) : 0.f;
+      wv[i] = (w_ok && k < K) ? to_f32(w_row[k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      As[lk + i][lrow] = av[i];
+      Ws[lk + i][lrow] = wv[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][ty * TM]);
+      const float4 w4 = *reinterpret_cast<const float4*>(&Ws[kk][tx * TN]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+      const float w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = ty * TM + i;
+    if (src_s[r] < 0) continue;
+    TC* c_row = C + (size_t)(tile * TILE + r) * ldc;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx * TN + j;
+      if (n < N) c_row[n] = from_f32<TC>(act_of(acc[i][j], act));
+    }
+  }
+}
+
+template <typename T>
+__global__ void combine_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ pair_slot,
+                               const float* __restrict__ weights, MaybePartial<T> shared, int top, int width, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width;
+    const int c = (int)(i - t * width);
+    float s = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int slot = pair_slot[t * top + j];
+      if (slot >= 0) s = fmaf(weights[t * top + j], y[(size_t)slot * width + c], s);
+    }
+    if (shared.present()) s += shared.at(i);
+    out[i] = from_f32<T>(s);
+  }
+}
+
+}  // namespace
+
+LLMK_API int llmk_moe_tile() { return TILE; }
+
+// h [n_tokens, h_stride] and w [experts, width] of the element kind, bias float32 [experts] or null;
+// ids int32 [n_tokens, top], weights float32 [n_tokens, top], both in the order of falling logits.
+LLMK_API int llmk_moe_route(const void* h, long long h_stride, const void* w, const float* bias, int* ids, float* weights,
+                            int n_tokens, int width, int experts, int top, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  LLMK_REQUIRE(experts > 0 && experts <= MAX_EXPERTS, "moe_route: %d experts (1 to %d)", experts, MAX_EXPERTS);
+  LLMK_REQUIRE(top > 0 && top <= experts, "moe_route: top %d of %d experts", top, experts);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(route_kernel<T>, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream,
+                  (const T*)h, h_stride, (const T*)w, bias, ids, weights, n_tokens, width, experts, top);
+    LLMK_LAUNCH_CHECK("moe_route");
+  });
+}
+
+// ids [n_pairs] -> meta[0] (tiles in use), tile_expert [max_tiles], slot_src [max_tiles * 64] (the pair of
+// a slot, -1 for padding), pair_slot [n_pairs].  max_tiles >= ceil(n_pairs / 64) + min(experts, n_pairs).
+LLMK_API int llmk_moe_group(const int* ids, int n_pairs, int experts, int* meta, int* tile_expert, int* slot_src,
+                            int* pair_slot, int max_tiles, cudaStream_t stream) {
+  if (n_pairs == 0) return 0;
+  LLMK_REQUIRE(experts > 0 && experts <= MAX_EXPERTS, "moe_group: %d experts (1 to %d)", experts, MAX_EXPERTS);
+  launch_kernel(group_kernel, dim3(1), dim3(1024), 0, stream, ids, n_pairs, experts, meta, tile_expert, slot_src, pair_slot,
+                max_tiles);
+  LLMK_LAUNCH_CHECK("moe_group");
+}
+
+// out_dtype: element kind of C (float32, or the input kind).  act: -1 none, else as llmk_act_rows.
+LLMK_API int llmk_moe_gemm(const void* A, long long lda, int gather_div, const int* slot_src, const int* tile_expert,
+                           const int* meta, const void* W, long long ldw, long long w_expert, void* C, long long ldc,
+                           int N, int K, int max_tiles, int act, int in_dtype, int out_dtype, cudaStream_t stream) {
+  if (max_tiles == 0 || N == 0) return 0;
+  LLMK_REQUIRE(K > 0 && lda >= K && ldw >= K && ldc >= N, "moe_gemm: bad sizes N=%d K=%d", N, K);
+  LLMK_REQUIRE(max_tiles <= 65535, "moe_gemm: %d tiles exceed the grid limit", max_tiles);
+  dim3 grid((N + BN - 1) / BN, max_tiles);
+#define LLMK_MOE_GEMM(T, TC)                                                                                        \
+  launch_kernel(grouped_gemm_kernel<T, TC>, grid, dim3(THREADS), 0, stream, (const T*)A, lda, gather_div, slot_src, \
+                tile_expert, meta, (const T*)W, ldw, w_expert, (TC*)C, ldc, N, K, act)
+  if (in_dtype == LLMK_F32 && out_dtype == LLMK_F32) LLMK_MOE_GEMM(float, float);
+  else if (in_dtype == LLMK_BF16 && out_dtype == LLMK_BF16) LLMK_MOE_GEMM(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == LLMK_BF16 && out_dtype == LLMK_F32) LLMK_MOE_GEMM(__nv_bfloat16, float);
+  else return llmk_fail(-1, "moe_gemm: unsupported element kinds in=%d out=%d", in_dtype, out_dtype);
+#undef LLMK_MOE_GEMM
+  LLMK_LAUNCH_CHECK("moe_gemm");
+}
+
+// out [n_tokens, width] of the element kind = shared (a tensor, partial results, or nothing) + the
+// weighted sum of the pairs' rows of y (float32 [slots, width]).
+LLMK_API int llmk_moe_combine(void* out, const float* y, const int* pair_slot, const float* weights, const void* shared,
+                              const float* partials, int splits, long long split_stride, int n_tokens, int top, int width,
+                              int dtype, cudaStream_t stream) {
+  const size_t total = (size_t)n_tokens * width;
+  if (total == 0) return 0;
+  LLMK_REQUIRE(!(shared && partials), "moe_combine: give shared or partials, not both");
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)llmk_sm_count() * 16) blocks = (size_t)llmk_sm_count() * 16;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> s{(const T*)shared, partials, splits, split_stride};
+    launch_kernel(combine_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, y, pair_slot, weights, s, top, width, total);
+    LLMK_LAUNCH_CHECK("moe_combine");
+  });
+}

@@ -247,3 +247,78 @@ LLMK_API int llmk_silu_mul(void* out, const void* gate_up, const float* partials
     LLMK_LAUNCH_CHECK("silu_mul");
   });
 }
+
+// ---- residual add + Dynamic Tanh ----------------------------------------------
+// resid += delta (if delta); out = tanh(alpha * resid) * w + b.  A norm without a mean or a
+// variance: every element stands alone, so the kernel is a plain sweep over rows * hidden.
+template <typename T>
+__global__ void add_dyt_kernel(float* __restrict__ resid, MaybePartial<T> delta, const float* __restrict__ w,
+                               const float* __restrict__ b, float alpha, T* __restrict__ out, int hidden, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const bool has_delta = delta.present();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float v = resid[i];
+    if (has_delta) {
+      v += delta.at(i);
+      resid[i] = v;
+    }
+    if (out) {
+      const int c = (int)(i % hidden);
+      out[i] = from_f32<T>(fmaf(tanhf(alpha * v), w[c], b[c]));
+    }
+  }
+}
+
+LLMK_API int llmk_add_dyt(float* resid, const void* delta, const float* partials, int splits, long long split_stride,
+                          const float* w, const float* b, float alpha, void* out, int rows, int hidden, int dtype,
+                          cudaStream_t stream) {
+  if (rows == 0) return 0;
+  LLMK_REQUIRE(!(delta && partials), "add_dyt: give delta or partials, not both");
+  const size_t total = (size_t)rows * hidden;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)llmk_sm_count() * 16) blocks = (size_t)llmk_sm_count() * 16;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> d{(const T*)delta, partials, splits, split_stride};
+    launch_kernel(add_dyt_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, resid, d, w, b, alpha, (T*)out, hidden, total);
+    LLMK_LAUNCH_CHECK("add_dyt");
+  });
+}
+
+// ---- element-wise activations -------------------------------------------------
+// out = act(in), float32 arithmetic; in a tensor or the partial results of a split-K product.
+// kind 0: relu(z)^2; 1: gelu with erf; 2: gelu with tanh; 3: z * sigmoid(z).
+enum : int { LLMK_ACT_RELU2 = 0, LLMK_ACT_GELU_ERF = 1, LLMK_ACT_GELU_TANH = 2, LLMK_ACT_SILU = 3 };
+
+__device__ __forceinline__ float apply_act(float z, int kind) {
+  switch (kind) {
+    case LLMK_ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
+    case LLMK_ACT_GELU_ERF: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+    case LLMK_ACT_GELU_TANH: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    default: return z / (1.f + expf(-z));
+  }
+}
+
+template <typename T>
+__global__ void act_rows_kernel(T* __restrict__ out, MaybePartial<T> in, int kind, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(apply_act(in.at(i), kind));
+}
+
+LLMK_API int llmk_act_rows(void* out, const void* in, const float* partials, int splits, long long split_stride,
+                           long long total, int kind, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  LLMK_REQUIRE((in != nullptr) != (partials != nullptr), "act_rows: give in or partials");
+  LLMK_REQUIRE(kind >= 0 && kind <= 3, "act_rows: unknown activation %d", kind);
+  size_t blocks = ((size_t)total + 255) / 256;
+  if (blocks > (size_t)llmk_sm_count() * 32) blocks = (size_t)llmk_sm_count() * 32;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> x{(const T*)in, partials, splits, split_stride};
+    launch_kernel(act_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, x, kind, (size_t)total);
+    LLMK_LAUNCH_CHECK("act_rows");
+  });
+}

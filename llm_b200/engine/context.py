@@ -36,6 +36,17 @@ class Workspace:
             self._buffers[key] = buf
         return buf[:rows]
 
+    def flat(self, tag: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A 1-D buffer of `numel` elements that is not sized by rows (lists of a routed feed-forward,
+        whose lengths follow the step limit times a part's constant); ask for the capacity, not for
+        what one step uses, so that the address stays fixed."""
+        key = (tag, -numel, dtype)
+        buf = self._buffers.get(key)
+        if buf is None:
+            buf = torch.zeros(numel, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 

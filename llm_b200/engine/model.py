@@ -62,7 +62,7 @@ class Model:
                 if key not in self.group_keys:
                     self.group_keys.append(key)
                 inst = len(self.cache_instances)
-                self.cache_instances.append(CacheInstance(self.group_keys.index(key), need.num_kv_heads, need.head_dim))
+                self.cache_instances.append(CacheInstance(self.group_keys.index(key), need.num_kv_heads, need.head_dim, need.values))
                 latest[layer_idx] = inst
             st = None
             if state is not None:
@@ -79,7 +79,8 @@ class Model:
         yield from walk(self.embedding)
         for block in self.blocks:
             for part in block.parts.values():
-                yield from walk(part)
+                if part is not None:
+                    yield from walk(part)
         if self.final_norm is not None:
             yield from walk(self.final_norm)
         yield from walk(self.head)

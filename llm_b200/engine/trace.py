@@ -27,7 +27,7 @@ def _parse_args(argv):
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens that live requests hold at any time (each rounded up to 64)")
     p.add_argument("--kv-block-size", type=int, default=16)
-    p.add_argument("--max-live", type=int, default=8, help="most requests alive at once")
+    p.add_argument("--max-live", type=int, default=4, help="most requests alive at once")
     return p.parse_args(argv)
 
 
@@ -42,11 +42,12 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     from .engine import Engine, StepEntry
 
     _arch, cfg = load_config(args.model)
-    max_pos = getattr(cfg, "max_position_embeddings")
     page = args.kv_block_size
     if args.max_tokens <= 0:
         raise SystemExit("--max-tokens must be positive")
     pool_tokens = (args.max_tokens + 63) // 64 * 64
+    # no request can hold more than the pool does; a model without a length limit of its own is sized by that
+    max_pos = min(getattr(cfg, "max_position_embeddings"), pool_tokens)
     per_step = min(max(pool_tokens, 64), 8192)
     options = EngineOptions(
         dtype=args.dtype, kv_block_size=page, max_num_seqs=args.max_live,

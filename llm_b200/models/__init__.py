@@ -1,4 +1,4 @@
-from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import llama, tevudra  # noqa: F401  (register LlamaForCausalLM, Tevudra)
 from .spec import LayerSpec, ModelSpec, PartSpec
 
 __all__ = ["LayerSpec", "ModelSpec", "PartSpec"]

@@ -58,6 +58,7 @@ class CacheNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True       # False: one vector per token serves as key and as value (a latent), so no value pages exist
 
     def group_key(self):
         return (self.kind, self.window)
@@ -81,6 +82,9 @@ class Part:
         self.device = device
 
     def name(self, local: str) -> str:
+        """prefix.local; an empty local name is the prefix itself (a tensor named like its part)."""
+        if not local:
+            return self.prefix
         return f"{self.prefix}.{local}" if self.prefix else local
 
     def parameters(self) -> Dict[str, ParamInfo]:

@@ -17,16 +17,18 @@ from .linear import linear
 class TokenEmbedding(Part):
     role = "embedding"
 
-    def __init__(self, vocab_size: int, hidden_size: int, prefix: str = "", dtype=None, device=None):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight", prefix: str = "", dtype=None,
+                 device=None):
         super().__init__(prefix, dtype, device)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.weight_name = weight_name        # "": the table is the tensor named like the part
         self.table = None
 
     def parameters(self):
-        return {self.name("weight"): ParamInfo((self.vocab_size, self.hidden_size))}
+        return {self.name(self.weight_name): ParamInfo((self.vocab_size, self.hidden_size))}
 
     def bind(self, tensors):
-        self.table = tensors[self.name("weight")].contiguous()
+        self.table = tensors[self.name(self.weight_name)].contiguous()
 
     def forward(self, ctx, stream: ResidualStream) -> None:
         ops.embedding(stream.resid, self.table, ctx.token_ids, ctx.n_tokens, ctx.status)
@@ -36,19 +38,20 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     role = "head"
 
-    def __init__(self, hidden_size: int, vocab_size: int, tied_to=None, prefix: str = "", dtype=None,
-                 device=None):
+    def __init__(self, hidden_size: int, vocab_size: int, tied_to=None, weight_name: str = "weight", prefix: str = "",
+                 dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         self.hidden_size, self.vocab_size, self.tied_to = hidden_size, vocab_size, tied_to
+        self.weight_name = weight_name        # "": the matrix is the tensor named like the part
         self.weight = None
 
     def parameters(self):
         if self.tied_to:
             return {}
-        return {self.name("weight"): ParamInfo((self.vocab_size, self.hidden_size))}
+        return {self.name(self.weight_name): ParamInfo((self.vocab_size, self.hidden_size))}
 
     def bind(self, tensors):
-        self.weight = tensors[self.tied_to if self.tied_to else self.name("weight")].contiguous()
+        self.weight = tensors[self.tied_to if self.tied_to else self.name(self.weight_name)].contiguous()
 
     def forward(self, rows: torch.Tensor, n_rows: int, out: torch.Tensor) -> torch.Tensor:
         return linear(rows, self.weight, out, n_rows)

@@ -59,3 +59,38 @@ class SwiGLU(Part):
 
 
 register_part("ffn", "swiglu", SwiGLU)
+
+
+class ActMLP(Part):
+    """down(act(up(x))): a feed-forward with one up-projection and an element-wise activation
+    ("relu2": the square of relu, "gelu": erf, "gelu_tanh", "silu").  Tensors `<prefix>.up` and
+    `<prefix>.down` unless other names are given."""
+
+    role = "ffn"
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2", up_name: str = "up",
+                 down_name: str = "down", prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward: unknown activation '{activation}'; known: {sorted(ops.ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.up_name, self.down_name = up_name, down_name
+        self.w_up = self.w_down = None
+
+    def parameters(self):
+        return {self.name(self.up_name): ParamInfo((self.intermediate_size, self.hidden_size)),
+                self.name(self.down_name): ParamInfo((self.hidden_size, self.intermediate_size))}
+
+    def bind(self, tensors):
+        self.w_up = tensors[self.name(self.up_name)].contiguous()
+        self.w_down = tensors[self.name(self.down_name)].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx, tag: str = "ffn") -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        up = linear(x, self.w_up, ws.get(tag + "_up", T, self.intermediate_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+        act = ws.get(tag + "_act", T, self.intermediate_size, self.dtype)
+        ops.act_rows(act, up, T, self.activation)
+        return linear(act, self.w_down, ws.get(tag + "_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+
+
+register_part("ffn", "mlp", ActMLP)

@@ -41,3 +41,44 @@ class RMSNorm(Part):
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class DynamicTanh(Part):
+    """y = tanh(alpha * x) * w + b: a norm that takes no mean and no variance, so every element
+    stands alone.  alpha is a scalar, w and b vectors; the tensors are `<prefix>` (w),
+    `<prefix>.b` and `<prefix>.alpha` unless other names are given.  The arithmetic is float32 on
+    the float32 residual, and the stream's pending term is added in the same pass."""
+
+    role = "norm"
+
+    def __init__(self, size: int, weight_name: str = "", bias_name: str = "b", alpha_name: str = "alpha",
+                 prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        self.size = size
+        self.names = (self.name(weight_name), self.name(bias_name), self.name(alpha_name))
+        self.w = self.b = None
+        self.alpha = 1.0
+
+    def parameters(self):
+        w, b, a = self.names
+        return {w: ParamInfo((self.size,), kind="gain", init="ones_normal"),
+                b: ParamInfo((self.size,), kind="gain", init="normal"),
+                a: ParamInfo((), kind="gain", init="ones_normal")}
+
+    def bind(self, tensors):
+        w, b, a = self.names
+        self.w, self.b = tensors[w].contiguous(), tensors[b].contiguous()
+        self.alpha = float(tensors[a].item())
+
+    def forward(self, stream: ResidualStream, ctx, tag: str = "normed") -> torch.Tensor:
+        out = ctx.workspace.get(tag, stream.rows, self.size, self.dtype)
+        ops.add_dyt(stream.resid, stream.pending, self.w, self.b, self.alpha, out, stream.rows)
+        stream.pending = None
+        return out
+
+    def forward_rows(self, rows_f32: torch.Tensor, n_rows: int, out: torch.Tensor) -> torch.Tensor:
+        ops.add_dyt(rows_f32, None, self.w, self.b, self.alpha, out, n_rows)
+        return out
+
+
+register_part("norm", "dyt", DynamicTanh)

@@ -1,0 +1,83 @@
+"""Routed feed-forward (mixture of experts) with an optional shared expert.
+
+  z      = Wr h + b                      float32
+  S      = the `top` experts with the largest z
+  w_e    = softmax over { z_e : e in S } (the chosen logits alone)
+  out    = sum_{e in S} w_e * down_e(act(up_e(h)))  +  down_s(act_s(up_s(h)))   (shared, if any)
+
+On the device: the router kernel writes each token's choices and weights; the (token, choice)
+pairs are sorted by expert into tiles of one expert each; the experts' up-projections run as
+one grouped product that gathers the tokens' rows and applies the activation; the
+down-projections as a second grouped product into float32; the last kernel sums a token's
+choices with their weights, in the order of the choices, and adds the shared expert.  Nothing
+on the host looks at the routing: every launch is sized by the numbers of tokens, choices and
+experts, so a step stays replayable from a CUDA graph.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import ParamInfo, Part, register_part
+from .feed_forward import ActMLP
+
+
+class RoutedFFN(Part):
+    role = "ffn"
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, activation: str = "gelu",
+                 router_bias: bool = True, shared_size: int = 0, shared_activation: str = None, prefix: str = "",
+                 dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if not (0 < top <= experts <= 256):
+            raise ValueError(f"routed feed-forward: top {top} of {experts} experts (1 <= top <= experts <= 256)")
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"routed feed-forward: unknown activation '{activation}'")
+        self.hidden_size, self.experts, self.top, self.expert_size = hidden_size, experts, top, expert_size
+        self.activation, self.router_bias = activation, bool(router_bias)
+        self.shared = (ActMLP(hidden_size, shared_size, shared_activation or activation, prefix=self.name("shared"),
+                              dtype=dtype, device=device) if shared_size else None)
+        self.w_router = self.b_router = self.w_up = self.w_down = None
+
+    def children(self):
+        return [self.shared] if self.shared is not None else []
+
+    def parameters(self):
+        p = {self.name("router"): ParamInfo((self.experts, self.hidden_size))}
+        if self.router_bias:
+            p[self.name("router.b")] = ParamInfo((self.experts,), kind="gain", init="normal")
+        for e in range(self.experts):
+            p[self.name(f"e{e}.up")] = ParamInfo((self.expert_size, self.hidden_size))
+            p[self.name(f"e{e}.down")] = ParamInfo((self.hidden_size, self.expert_size))
+        return p
+
+    def bind(self, tensors):
+        self.w_router = tensors[self.name("router")].contiguous()
+        self.b_router = tensors[self.name("router.b")].contiguous() if self.router_bias else None
+        self.w_up = torch.stack([tensors[self.name(f"e{e}.up")] for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[self.name(f"e{e}.down")] for e in range(self.experts)]).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        T, ws, top, E = ctx.n_tokens, ctx.workspace, self.top, self.experts
+        pairs, tile = T * top, ops.moe_tile()
+        max_tiles = ops.moe_max_tiles(pairs, E)                       # of this step: a function of T alone
+        cap_pairs = ws.max_rows * top
+        cap_slots = ops.moe_max_tiles(cap_pairs, E) * tile            # of any step: the buffers' sizes
+        i32, f32 = torch.int32, torch.float32
+        ids, wts = ws.flat("moe_ids", cap_pairs, i32), ws.flat("moe_weights", cap_pairs, f32)
+        pair_slot, meta = ws.flat("moe_pair_slot", cap_pairs, i32), ws.flat("moe_meta", 4, i32)
+        tile_expert, slot_src = ws.flat("moe_tile_expert", cap_slots // tile, i32), ws.flat("moe_slot_src", cap_slots, i32)
+        act = ws.flat("moe_act", cap_slots * self.expert_size, self.dtype).view(cap_slots, self.expert_size)
+        y = ws.flat("moe_y", cap_slots * self.hidden_size, f32).view(cap_slots, self.hidden_size)
+
+        ops.moe_route(x, self.w_router, self.b_router, ids, wts, T, top)
+        ops.moe_group(ids, pairs, E, meta, tile_expert, slot_src, pair_slot, max_tiles)
+        ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, act, max_tiles, act=self.activation)
+        ops.moe_gemm(act, 0, slot_src, tile_expert, meta, self.w_down, y, max_tiles)
+        shared = self.shared.forward(x, ctx, tag="ffn_shared") if self.shared is not None else None
+        out = ws.get("ffn_out", T, self.hidden_size, self.dtype)
+        ops.moe_combine(out, y, pair_slot, wts, shared, T, top)
+        return out
+
+
+register_part("ffn", "routed", RoutedFFN)
