@@ -87,9 +87,20 @@ def routed_ff(h, w_r, b_r, top: int, experts: List[tuple], shared: Optional[tupl
     return out
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, keep_layers: bool = False):
+def route_margin(h, w_r, b_r, top: int) -> torch.Tensor:
+    """Per token, how far the last chosen logit lies above the first one left out (inf if all are chosen):
+    where this is small, a rounding error elsewhere can change the choice."""
+    z = h.to(F64) @ w_r.to(F64).T + b_r.to(F64)
+    if top >= z.shape[1]:
+        return torch.full((z.shape[0],), math.inf, dtype=F64)
+    s = torch.sort(z, dim=-1, descending=True).values
+    return s[:, top - 1] - s[:, top]
+
+
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, keep_layers: bool = False, margins: Optional[list] = None):
     """Logits [T, vocab] in float64 of one whole sequence; with keep_layers also the residual
-    stream after every layer [layers, T, W]."""
+    stream after every layer [layers, T, W].  margins: a list that receives, per routed layer, the
+    tokens' route_margin."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"].to(F64)[torch.as_tensor(tokens, dtype=torch.long)]
     latents: Dict[int, torch.Tensor] = {}
@@ -117,6 +128,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, keep_layers: bool = F
                 n, top = ff["router"]["experts"], ff["router"]["top"]
                 experts = [(w[f"{p}.mlp.e{e}.up"], w[f"{p}.mlp.e{e}.down"]) for e in range(n)]
                 shared = (w[p + ".mlp.shared.up"], w[p + ".mlp.shared.down"]) if ff.get("shared") else None
+                if margins is not None:
+                    margins.append(route_margin(h, w[p + ".mlp.router"], w[p + ".mlp.router.b"], top))
                 x = x + routed_ff(h, w[p + ".mlp.router"], w[p + ".mlp.router.b"], top, experts, shared)
             else:
                 raise ValueError(ff["kind"])

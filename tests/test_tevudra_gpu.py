@@ -1,0 +1,359 @@
+"""GPU tests of the Tevudra design against the plain implementation (tests/plain_tevudra.py):
+each mechanism alone, then whole models under every way of cutting the work."""
+import math
+import types
+
+import pytest
+import torch
+
+import plain_tevudra as P
+import replay
+from tevudra_tiny import CONFIGS, make_engine, make_weights
+from tiny import max_err, random_tokens
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# whole models, relative to the largest logit: rounding only in 32-bit; in bfloat16 every product's output is
+# rounded to 8 bits, and a latent attention has two more products per layer (into and out of the latent space)
+# than a plain one
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# kernels alone: what one rounding of the output to bfloat16 allows, relative to the largest value
+KTOL = {"float32": 3e-6, "bfloat16": 6e-3}
+
+
+def dev(t, dtype="float32"):
+    return t.to(device="cuda", dtype=DT[dtype]).contiguous()
+
+
+def bf(t):
+    """Values that bfloat16 holds exactly, as float32."""
+    return t.to(torch.bfloat16).float()
+
+
+# ---- each mechanism alone ---------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,width", [(1, 8), (7, 100), (33, 192)])
+def test_dynamic_tanh_with_pending_term(dtype, rows, width):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(rows * 1000 + width)
+    x, d = torch.randn(rows, width, generator=g) * 3, bf(torch.randn(rows, width, generator=g))
+    w, b, alpha = 1 + 0.2 * torch.randn(width, generator=g), torch.randn(width, generator=g), 0.37
+    resid, out = dev(x), torch.empty(rows, width, device="cuda", dtype=DT[dtype])
+    ops.add_dyt(resid, dev(d, dtype), dev(w), dev(b), alpha, out, rows)
+    assert max_err(resid, x + d) < 1e-6
+    assert max_err(out, P.dyt(x.double() + d.double(), alpha, w, b)) < KTOL[dtype]
+    ops.add_dyt(resid, None, dev(w), dev(b), alpha, out, rows)          # nothing pending: the stream stays
+    assert max_err(resid, x + d) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_activations(dtype):
+    from llm_b200.csrc import ops
+    z = bf(torch.linspace(-6, 6, 6 * 50).view(6, 50))
+    ref = {"relu2": torch.relu(z.double()) ** 2, "gelu": P.gelu_erf(z.double()),
+           "gelu_tanh": 0.5 * z.double() * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z.double() + 0.044715 * z.double() ** 3))),
+           "silu": z.double() * torch.sigmoid(z.double())}
+    for kind, want in ref.items():
+        out = torch.empty(6, 50, device="cuda", dtype=DT[dtype])
+        ops.act_rows(out, dev(z, dtype), 6, kind)
+        assert max_err(out, want) < KTOL[dtype], kind
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rank", [8, 24, 96, 320])
+def test_latent_norm_and_store(dtype, rank):
+    """The cached vector against rms(x) * gain, written to shuffled places of the pages."""
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(rank)
+    T, page, pages = 21, 8, 6
+    x = bf(torch.randn(T, rank + 5, generator=g) * 2)           # the projection is the first `rank` columns of wider rows
+    gain, eps = 1 + 0.3 * torch.randn(rank, generator=g), 1e-3
+    slots = torch.randperm(page * pages, generator=g)[:T].to(torch.int32)
+    store = torch.zeros(pages, 1, page, rank, device="cuda", dtype=DT[dtype])
+    ops.latent_norm_store(dev(x, dtype)[:, :rank], dev(gain), eps, slots.cuda(), store, T)
+    want = P.rms(x[:, :rank], gain, eps)
+    got = store.view(-1, rank)[slots.long().cuda()]
+    assert max_err(got, want) < KTOL[dtype]
+    untouched = torch.ones(page * pages, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert float(store.view(-1, rank)[untouched.cuda()].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,n,k,rows", [(1, 8, 8, 1), (3, 24, 16, 5), (8, 96, 32, 70), (2, 20, 320, 9)])
+def test_per_head_products_with_gate(dtype, heads, n, k, rows):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(heads * 100 + n)
+    a, w = bf(torch.randn(rows, heads * k, generator=g)), bf(torch.randn(heads, n, k, generator=g) / math.sqrt(k))
+    wide = bf(torch.randn(rows, heads + 3, generator=g) * 2)     # the gate's logits are columns 3.. of wider rows
+    want = torch.einsum("thk,hnk->thn", a.double().view(rows, heads, k), w.double())
+    out = torch.empty(rows, heads * n, device="cuda", dtype=DT[dtype])
+    ops.gemm_heads(dev(a, dtype), dev(w, dtype), out, rows, heads)
+    assert max_err(out, want.reshape(rows, -1)) < KTOL[dtype]
+    ops.gemm_heads(dev(a, dtype), dev(w, dtype), out, rows, heads, gate=dev(wide, dtype)[:, 3:])
+    gated = want * torch.sigmoid(wide.double()[:, 3:])[:, :, None]
+    assert max_err(out, gated.reshape(rows, -1)) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("experts,top", [(1, 1), (4, 2), (3, 3), (8, 1), (37, 5)])
+def test_router_choices_and_weights(dtype, experts, top):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(experts * 10 + top)
+    T, W = 19, 48
+    h, wr, b = bf(torch.randn(T, W, generator=g)), bf(torch.randn(experts, W, generator=g)), torch.randn(experts, generator=g)
+    ids = torch.zeros(T, top, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(T, top, dtype=torch.float32, device="cuda")
+    ops.moe_route(dev(h, dtype), dev(wr, dtype), dev(b), ids, wts, T, top)
+    want_ids, want_w = P.route(h, wr, b, top)
+    assert torch.equal(ids.cpu().long(), want_ids)
+    assert max_err(wts, want_w) < 1e-5
+    assert float((wts.sum(1) - 1).abs().max()) < 1e-5
+
+
+def _fake_ctx(rows, max_rows=64):
+    from llm_b200.engine.context import Workspace
+    return types.SimpleNamespace(n_tokens=rows, workspace=Workspace(max_rows, torch.device("cuda")))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("experts,top,ff,shared,rows", [(4, 2, 40, 48, 13), (3, 3, 16, 0, 5), (8, 1, 64, 32, 1), (5, 2, 24, 72, 64),
+                                                        (2, 1, 8, 0, 150)])
+def test_routed_feed_forward_part(dtype, experts, top, ff, shared, rows):
+    """The whole routed feed-forward (router, grouping, both grouped products, weighted sum, shared
+    expert) as the part runs it; 150 rows of one or two experts fill more than one tile each."""
+    from llm_b200.parts.routed import RoutedFFN
+    g = torch.Generator().manual_seed(experts * 7 + rows)
+    W = 32
+    part = RoutedFFN(W, experts, top, ff, "gelu", True, shared, prefix="m", dtype=DT[dtype], device=torch.device("cuda"))
+    w = {}
+    for name, info in list(part.parameters().items()) + (list(part.shared.parameters().items()) if shared else []):
+        w[name] = bf(torch.randn(*info.shape, generator=g) * (0.5 if name.endswith(".b") else 1.5 / math.sqrt(info.shape[-1])))
+    on_dev = {n: dev(t, "float32" if n.endswith("router.b") else dtype) for n, t in w.items()}
+    part.bind(on_dev)
+    if shared:
+        part.shared.bind(on_dev)
+    h = bf(torch.randn(rows, W, generator=g))
+    ctx = _fake_ctx(rows, max_rows=160)
+    out = part.forward(dev(h, dtype), ctx).clone()
+    want = P.routed_ff(h, w["m.router"], w["m.router.b"], top, [(w[f"m.e{e}.up"], w[f"m.e{e}.down"]) for e in range(experts)],
+                       (w["m.shared.up"], w["m.shared.down"]) if shared else None)
+    assert max_err(out, want) < (1e-5 if dtype == "float32" else 1.5e-2)
+    again = part.forward(dev(h, dtype), ctx).clone()              # slots may be dealt differently; the values may not change
+    assert torch.equal(out, again)
+
+
+# ---- whole models, every way of cutting the work --------------------------------------------
+LENGTHS = {"P": [1, 5, 33, 70, 129], "Q": [2, 47, 64, 150, 260], "R": [3, 40, 17, 90], "S": [1, 16, 31, 100]}
+
+
+@pytest.fixture(scope="module")
+def models():
+    cache = {}
+
+    def get(name):
+        if name not in cache:
+            cfg, page = CONFIGS[name]
+            w = make_weights(cfg, seed=ord(name))
+            reqs = {f"r{i}": random_tokens(n, cfg["vocab"], 300 + i) for i, n in enumerate(LENGTHS[name])}
+            ref = {rid: plain_with_margin(cfg, w, toks) for rid, toks in reqs.items()}
+            cache[name] = (cfg, page, w, reqs, ref)
+        return cache[name]
+    return get
+
+
+class Ref(torch.Tensor):
+    """Plain logits that also carry, per row, the smallest routing margin of the token (see
+    plain_tevudra.route_margin)."""
+
+
+def plain_with_margin(cfg, w, toks):
+    margins = []
+    ref = P.forward(cfg, w, toks, margins=margins).as_subclass(Ref)
+    ref.margin = torch.stack(margins).min(0).values if margins else torch.full((len(toks),), math.inf, dtype=torch.float64)
+    return ref
+
+
+# In bfloat16 the router reads a rounded input, so a token whose last chosen logit lies this close to
+# the first one left out may be routed differently than in float64; such rows prove nothing and are
+# left out of the comparison (they are few, which is asserted).  Float32 compares every row.
+CLOSE_CALL = {"float32": 0.0, "bfloat16": 0.1}
+
+
+def compare(got, ref, dtype, what):
+    for rid, r in ref.items():
+        assert got[rid].shape == r.shape, f"{what}: {rid} shape {got[rid].shape} vs {r.shape}"
+        err_rows = (got[rid].double() - r).abs().max(dim=1).values / r.abs().max()
+        margin = getattr(r, "margin", None)
+        if margin is not None:
+            unclear = margin < CLOSE_CALL[dtype]
+            assert int(unclear.sum()) <= max(2, len(unclear) // 4), f"{what}: too many close routing calls to compare {rid}"
+            err_rows = torch.where(unclear, torch.zeros_like(err_rows), err_rows)
+        bad = torch.nonzero(err_rows > TOL[dtype])
+        assert bad.numel() == 0, (f"{what}: request {rid} first differs at position {int(bad[0])} "
+                                  f"(err {float(err_rows[int(bad[0])]):.3e}, limit {TOL[dtype]:.1e})")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
+def test_every_cut_matches_plain(models, name, dtype):
+    cfg, page, w, reqs, ref = models(name)
+    longest = max(len(t) for t in reqs.values())
+    eng = make_engine(cfg, w, dtype, page, -(-longest // page) + 1)       # a pool barely larger than the longest request
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, "whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs)), ref, dtype, "tail decode")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs)), ref, dtype, "portions")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs, sizes=(2, 2, 3, 2, 16, 2, 17, 64))), ref, dtype, "small portions")
+    eng.cache.check()
+    assert all(eng.cache.num_free_pages(g) == eng.cache.group_spec(g).num_pages for g in range(eng.cache.num_groups))
+    lens = sorted((len(t) for t in reqs.values()), reverse=True)
+    eng = make_engine(cfg, w, dtype, page, sum(-(-n // page) for n in lens[:4]) + 1)
+    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, "mixed")     # freed pages are used again
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batch_of_unequal_requests_equals_each_alone(models, dtype):
+    from llm_b200.engine.engine import StepEntry
+    cfg, page, w, reqs, ref = models("P")
+    eng = make_engine(cfg, w, dtype, page, 40)
+    alone = replay.run_steps(eng, replay.steps_whole(reqs))
+    entries = [StepEntry(rid, toks, list(range(len(toks)))) for rid, toks in reqs.items() if len(toks) < 129][:4]
+    rows = eng.step(entries).float().cpu()
+    at = 0
+    for e in entries:
+        n = len(e.tokens)
+        clear = ref[e.request_id].margin >= CLOSE_CALL[dtype]
+        assert max_err(rows[at:at + n][clear], alone[e.request_id][clear]) < (1e-5 if dtype == "float32" else 2e-2)
+        at += n
+        eng.release(e.request_id)
+
+
+# ---- one key that carries the row: far back, at page borders, at the causal edge ---------------
+def _needle_model(beta=40.0):
+    """Configuration S (one layer, the mixer alone) with the query projection changed so that the
+    token QUERY looks for the token NEEDLE: Wq += beta * k(needle) h(query)^T / |h(query)|^2 per head.
+    Without positions and in the first layer, a token's query, key and value depend on its id
+    alone, so the score of (QUERY, NEEDLE) stands out by about beta * |k|^2 * scale wherever the two are."""
+    cfg, page = CONFIGS["S"]
+    w = make_weights(cfg, seed=9, peak=0.5)
+    needle, query = 7, 11
+    m = cfg["layers"][0]["mixer"]
+    norm = lambda tok: P.dyt(w["embed"][tok].double(), w["l0.norm1.alpha"], w["l0.norm1"], w["l0.norm1.b"])
+    h_n, h_q = norm(needle), norm(query)
+    c_n = P.latent(h_n[None], w["l0.mix.dkv"], w["l0.mix.dkv.norm"], cfg["norm"]["eps"])[0]
+    k_n = w["l0.mix.uk"].double() @ c_n                                   # [heads * dim]
+    k_n = k_n.view(m["heads"], m["dim"])
+    k_n = (k_n / k_n.norm(dim=1, keepdim=True)).reshape(-1)
+    w["l0.mix.q"] = bf((w["l0.mix.q"].double() + beta * torch.outer(k_n, h_q) / (h_q @ h_q)).float())
+    return cfg, page, w, needle, query
+
+
+def _needle_tokens(cfg, n, needles, queries, seed):
+    toks = [t for t in random_tokens(3 * n, cfg["vocab"], seed) if t not in (7, 11)][:n]
+    for p in needles:
+        toks[p] = 7
+    for p in queries:
+        toks[p] = 11
+    return toks
+
+
+NEEDLE_CASES = {      # name: (length, needle positions, query positions); pages hold 16 tokens
+    "first_token": (300, [0], [1, 15, 16, 17, 150, 299]),
+    "page_borders": (200, [15], [16, 17, 31, 32, 33, 199]),
+    "page_start": (200, [16], [17, 18, 47, 48, 49, 198]),
+    "page_second": (200, [17], [18, 32, 64, 65, 197]),
+    "far_among_hundreds": (700, [203], [204, 208, 512, 640, 698, 699]),
+    "not_yet_visible": (120, [60], [10, 58, 59, 61, 62, 119]),        # queries before the needle must not see it
+    "self_only": (90, [], [0, 1, 16, 89]),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", sorted(NEEDLE_CASES))
+def test_one_key_carries_the_row(dtype, case):
+    cfg, page, w, needle, query = _needle_model()
+    n, needles, queries = NEEDLE_CASES[case]
+    toks = _needle_tokens(cfg, n, needles, queries, seed=len(case))
+    ref = P.forward(cfg, w, toks)
+    if needles:
+        # the test's premise: without the needle the logits at the later queries are far off
+        blind = list(toks)
+        for p in needles:
+            blind[p] = 3
+        other = P.forward(cfg, w, blind)
+        seen = [q for q in queries if q > needles[0]]
+        gap = ((ref[seen] - other[seen]).abs().max(dim=1).values / ref.abs().max()).min()
+        assert float(gap) > 6 * TOL[dtype], f"the needle does not stand out ({float(gap):.2e})"
+    reqs, refs = {"n": toks}, {"n": ref}
+    eng = make_engine(cfg, w, dtype, page, -(-n // page) + 2, max_tokens=768)
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), refs, dtype, "whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs, tail=min(n - 1, 190))), refs, dtype, "decode")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs, sizes=(2, 14, 1, 16, 3, 29, 2, 64, 5))), refs, dtype, "portions")
+    eng.cache.check()
+
+
+# ---- long decoding and generation through the scheduler --------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_long_decode_with_graphs_and_first_tokens(models, name, dtype):
+    from llm_b200.engine.engine import StepEntry
+    cfg, page, w, _reqs, _ref = models(name)
+    toks = random_tokens(210, cfg["vocab"], 77)
+    ref = plain_with_margin(cfg, w, toks)
+    eng = make_engine(cfg, w, dtype, page, -(-210 // page) + 1, max_tokens=64, max_seqs=2, poison=False, graphs=True)
+    rows = [eng.step([StepEntry("x", toks[:2], [0, 1])]).double().cpu().clone()]
+    for t in toks[2:]:
+        rows.append(eng.step([StepEntry("x", [t], [0])]).double().cpu().clone())
+    eng.check_status()
+    compare({"x": torch.cat(rows)}, {"x": ref}, dtype, "long decode")
+    assert eng.counters["graph_replays"] > 100
+
+
+def _plain_greedy(cfg, w, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(torch.argmax(P.forward(cfg, w, ids)[-1])))
+    return ids[len(prompt):]
+
+
+def test_greedy_generation_through_the_scheduler(models):
+    from llm_b200 import LLM
+    cfg, page, w, _reqs, _ref = models("P")
+    prompts = [random_tokens(n, cfg["vocab"], 500 + n) for n in (1, 9, 30, 47, 18)]
+    llm = LLM(None, dtype="float32", max_num_seqs=3, max_num_batched_tokens=16, kv_block_size=page, num_kv_blocks=14,
+              eos_token_id=-1, random_config=cfg, tensors={k: v.clone() for k, v in w.items()}, max_seq_len=128)
+    got = llm.generate(prompts, max_new_tokens=20)
+    for p, g in zip(prompts, got):
+        assert g == _plain_greedy(cfg, w, p, 20)
+    llm.engine.cache.check()
+
+
+def test_trace_replay_of_a_folder(models, tmp_path):
+    """A model folder written to disk and replayed through the trace runner's entry point."""
+    import io
+    import json
+    import numpy as np
+    from llm_b200.engine import trace
+    from llm_b200.weights.safetensors_io import write_safetensors
+    cfg, page, w, reqs, ref = models("P")
+    d = tmp_path / "model"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(d / "model.safetensors"), {k: (v.to(torch.bfloat16) if v.dim() == 2 else v) for k, v in w.items()})
+    lines, want = [], {}
+    for n, st in enumerate(replay.steps_mixed({k: v for k, v in reqs.items() if len(v) > 1})):
+        lines.append(json.dumps({"step": n, **st}))
+        want[n] = [(e["id"], len(e["want"])) for e in st["entries"]]
+    out = io.StringIO()
+    assert trace.main(["--model", str(d), "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "512"],
+                      stdin=io.StringIO("\n".join(lines) + "\n"), stdout=out) == 0
+    assert out.getvalue().split() == [x for n in range(len(lines)) for x in ("done", str(n))]
+    at = {rid: 0 for rid in reqs}
+    for n, rows in want.items():
+        got = torch.from_numpy(np.fromfile(tmp_path / "o" / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+        r = 0
+        for rid, k in rows:
+            assert max_err(got[r:r + k], ref[rid][at[rid]:at[rid] + k]) < 1e-4
+            at[rid] += k
+            r += k
