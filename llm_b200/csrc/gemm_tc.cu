@@ -101,6 +101,35 @@ __device__ __forceinline__ int tile_col0(int col0, int width, int limit) { retur
 // error codes written to *err_flag: which wait gave up
 enum : int { ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3 };
 
+// Several products of the same sizes in one launch of the one-tile kernel (normal mode, no split of K).
+//   by_z     product g = blockIdx.z reads columns g * a_k_step .. of A and rows g * w_row_step .. of W
+//            and writes columns g * (the kernel's split_stride) .. of C: the per-head maps of a
+//            latent attention, whose heads lie side by side in a row.
+//   by_tile  row tile blockIdx.x belongs to group tile_group[blockIdx.x] and multiplies by rows
+//            g * w_row_step .. of W; tiles from *n_tiles on do nothing: the experts of a routed
+//            feed-forward over rows that were sorted by expert, each expert's run padded to whole tiles.
+// act: an activation on the float32 accumulator before the store (-1 none; 0 relu^2, 1 gelu erf,
+// 2 gelu tanh, 3 silu).  gate (by_z): row p of product g is multiplied by sigmoid(gate[p, g]).
+struct Grouping {
+  int mode;                      // 0 none, 1 by_z, 2 by_tile
+  int a_k_step, w_row_step;
+  const int* tile_group;
+  const int* n_tiles;
+  int act;
+  const __nv_bfloat16* gate;
+  long long gate_stride;
+};
+
+__device__ __forceinline__ float epilogue_act(float z, int kind) {
+  switch (kind) {
+    case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 1: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+    case 2: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    case 3: return z / (1.f + expf(-z));
+    default: return z;
+  }
+}
+
 // CLUSTER (swapped mode only): the CTAs that split K for one tile form a thread-block cluster
 // along blockIdx.z.  Instead of writing float32 partial results to global memory for a later
 // kernel to sum, each CTA hands its accumulator to the first CTA of the cluster through
@@ -109,7 +138,7 @@ template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                TOut* __restrict__ C, long long ldc, long long split_stride, int M, int N, int K,
-               int kblocks_per_split, int tile_q, int* __restrict__ err_flag) {
+               int kblocks_per_split, int tile_q, int* __restrict__ err_flag, const Grouping grp) {
   // BNQ sizes the stages and the tensor memory; tile_q <= BNQ (a multiple of 32, or 16 = BNQ) is
   // the width actually computed, chosen on the host so that the grid fills whole waves.
   constexpr int STAGES = stages_for(BNQ, SWAP);
@@ -132,11 +161,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int group = 0;
+  if (grp.mode == 2) {
+    // which tiles are in use is what the kernel before this one wrote: wait for it first
+    pdl_wait();
+    if ((int)blockIdx.x >= *grp.n_tiles) return;
+    group = grp.tile_group[blockIdx.x];
+  } else if (grp.mode == 1) {
+    group = blockIdx.z;
+  }
   const int p0 = tile_row0(blockIdx.x * BP, SWAP ? N : M);
   const int q0 = SWAP ? blockIdx.y * tile_q : tile_col0(blockIdx.y * tile_q, tile_q, N);
   const int total_kb = (K + BK - 1) / BK;
-  const int kb_begin = blockIdx.z * kblocks_per_split;
+  const int kb_begin = grp.mode ? 0 : blockIdx.z * kblocks_per_split;
   const int kb_end = min(total_kb, kb_begin + kblocks_per_split);
+  const int a_k0 = grp.mode == 1 ? group * grp.a_k_step : 0;       // first column of A of this product
   const int nkb = max(0, kb_end - kb_begin);
   C += (long long)blockIdx.z * split_stride;
   float acc[CLUSTER ? BNQ : 1];          // the accumulator row of an epilogue thread, kept across the cluster barriers
@@ -153,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   const CUtensorMap* map_a = SWAP ? &map_q : &map_p;
   constexpr int W_STAGE = SWAP ? P_STAGE_BYTES : Q_STAGE_BYTES;
   constexpr int A_STAGE = SWAP ? Q_STAGE_BYTES : P_STAGE_BYTES;
-  const int w0 = SWAP ? p0 : q0, a0 = SWAP ? q0 : p0;
+  const int w0 = (SWAP ? p0 : q0) + group * grp.w_row_step, a0 = SWAP ? q0 : p0;
   const int pre = min(nkb, STAGES);
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -180,7 +219,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       // ---- producer: TMA loads into the ring ----
       pdl_wait();
       for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem_a + i * A_STAGE, map_a, (kb_begin + i) * BK, a0, &full_bar[i]);
+        tma_load_2d(smem_a + i * A_STAGE, map_a, a_k0 + (kb_begin + i) * BK, a0, &full_bar[i]);
       int issued = pre;
       bool ok = true;
       for (int i = pre; i < nkb && ok; ++i) {
@@ -191,7 +230,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         mbar_arrive_expect_tx(&full_bar[s], stage_tx);
         const int k = (kb_begin + i) * BK;
         tma_load_2d(smem_w + s * W_STAGE, map_w, k, w0, &full_bar[s]);
-        tma_load_2d(smem_a + s * A_STAGE, map_a, k, a0, &full_bar[s]);
+        tma_load_2d(smem_a + s * A_STAGE, map_a, a_k0 + k, a0, &full_bar[s]);
         issued = i + 1;
       }
       if (!ok) {
@@ -279,6 +318,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       }
       if (p >= p_limit) continue;
       const int q = q0 + c;
+      if (!SWAP && grp.act >= 0) {
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) v[j] = epilogue_act(v[j], grp.act);
+      }
+      if (!SWAP && grp.gate) {
+        const float g = 1.f / (1.f + expf(-__bfloat162float(grp.gate[(long long)p * grp.gate_stride + group])));
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) v[j] *= g;
+      }
       if (SWAP) {
         // thread holds C[m = q + j][n = p]: neighbouring lanes are neighbouring n
 #pragma unroll
@@ -880,7 +928,8 @@ int ensure_err_flag() {
 
 template <int BNQ, bool SWAP, typename TOut, bool CLUSTER>
 int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, long long split_stride, int M,
-               int N, int K, int splits, int kb_per_split, int tile_q, cudaStream_t stream) {
+               int N, int K, int splits, int kb_per_split, int tile_q, cudaStream_t stream,
+               const Grouping grp = Grouping{0, 0, 0, nullptr, nullptr, -1, nullptr, 0}) {
   auto kern = gemm_tc_kernel<BNQ, SWAP, TOut, CLUSTER>;
   constexpr int smem = smem_bytes_for(BNQ, SWAP);
   static bool configured = false;
@@ -906,9 +955,9 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = llmk_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, tile_q, g_err_flag);
+    cudaLaunchKernelEx(&cfg, kern, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, tile_q, g_err_flag, grp);
   } else {
-    launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, tile_q, g_err_flag);
+    launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, split_stride, M, N, K, kb_per_split, tile_q, g_err_flag, grp);
   }
   LLMK_LAUNCH_CHECK("gemm_tc");
 }
@@ -1084,6 +1133,40 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   if (out_dtype == LLMK_F32) return launch_out<float>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
   if (out_dtype == LLMK_BF16) return launch_out<__nv_bfloat16>(swap != 0, tile, cluster != 0, mp, mq, C, ldc, split_stride, M, N, K, splits, kblocks_per_split, stream);
   return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
+}
+
+// Several products in one launch of the one-tile kernel (see Grouping).  A and W bfloat16.
+// mode 1 (by_z): A [M, groups * a_k_step] (K <= a_k_step columns of a group are used), W [groups * N, K],
+//   C [M, >= groups * c_step] (group g writes N columns from g * c_step); gate [M, gate_stride] or null.
+// mode 2 (by_tile): A [M, K] with M a multiple of 128 (rows sorted by group, runs padded to whole tiles),
+//   W [groups * N, K], C [M, ldc]; tile_group [M / 128] and n_tiles [1] on the device.
+LLMK_API int llmk_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
+                                  long long ldc, int out_dtype, int mode, int groups, int a_k_step, long long c_step,
+                                  const int* tile_group, const int* n_tiles, int act, const void* gate,
+                                  long long gate_stride, cudaStream_t stream) {
+  if (M == 0 || N == 0 || groups == 0) return 0;
+  LLMK_REQUIRE(mode == 1 || mode == 2, "gemm_tc_grouped: mode %d (1 = by product, 2 = by row tile)", mode);
+  LLMK_REQUIRE(llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw), "gemm_tc_grouped: K=%d and the row pitches must be multiples of 8 and the bases 16-byte aligned", K);
+  LLMK_REQUIRE(mode != 1 || (a_k_step % 8 == 0 && K <= a_k_step && groups <= 65535), "gemm_tc_grouped: a_k_step %d must be a multiple of 8 and at least K=%d", a_k_step, K);
+  LLMK_REQUIRE(mode != 2 || (M % BP == 0 && tile_group && n_tiles), "gemm_tc_grouped: by_tile needs M=%d a multiple of %d and the tile table", M, BP);
+  LLMK_REQUIRE(act >= -1 && act <= 3, "gemm_tc_grouped: unknown activation %d", act);
+  int rc = ensure_err_flag();
+  if (rc) return rc;
+  // the tile of weight rows: as wide as the product where that is at most 256 (in steps of 32), else 256 or 128
+  int tile = (N + 31) / 32 * 32;
+  if (tile > 256) tile = (N % 256 == 0 || N % 256 > 128) ? 256 : 128;
+  CUtensorMap mp, mq;
+  if ((rc = get_map(&mp, A, M, mode == 1 ? (uint64_t)groups * a_k_step : (uint64_t)K, lda, M < BP ? M : BP))) return rc;
+  if ((rc = get_map(&mq, W, (uint64_t)groups * N, K, ldw, tile))) return rc;
+  const Grouping grp{mode, a_k_step, N, tile_group, n_tiles, act, (const __nv_bfloat16*)gate, gate_stride};
+  const int splits = mode == 1 ? groups : 1;            // the grid's z: one product each
+  const int kb = (K + BK - 1) / BK;
+  const long long step = mode == 1 ? c_step : 0;
+#define LLMK_GROUPED(BNQ, TOut) launch_cfg<BNQ, false, TOut, false>(mp, mq, C, ldc, step, M, N, K, splits, kb, tile, stream, grp)
+  if (out_dtype == LLMK_F32) return tile <= 128 ? LLMK_GROUPED(128, float) : LLMK_GROUPED(256, float);
+  if (out_dtype == LLMK_BF16) return tile <= 128 ? LLMK_GROUPED(128, __nv_bfloat16) : LLMK_GROUPED(256, __nv_bfloat16);
+#undef LLMK_GROUPED
+  return llmk_fail(-1, "gemm_tc_grouped: unsupported output kind %d", out_dtype);
 }
 
 // Whether llmk_gemm_tc_qkv_rope takes these sizes and pointers.

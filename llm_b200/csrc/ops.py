@@ -174,6 +174,9 @@ def act_rows(out: torch.Tensor, x, rows: int, kind: str) -> None:
                                 c_int(_kind(out.dtype)), _stream()))
 
 
+HEADS_ON_TENSOR_CORES = True
+
+
 def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, heads: int, gate=None) -> None:
     """Per-head products in one launch: out[:, h*N:(h+1)*N] = a[:, h*K:(h+1)*K] @ w[h].T for w [heads, N, K];
     with a gate [rows, >= heads] (a view with unit column stride) head h of a row is multiplied by
@@ -185,6 +188,14 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, h
     if gate is not None:
         _rows_contig(gate, "gate")
         assert gate.dtype == a.dtype and gate.shape[1] >= heads
+    if (HEADS_ON_TENSOR_CORES and a.dtype == torch.bfloat16 and rows >= NORMAL_MODE_FROM_ROWS and k % 8 == 0
+            and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        # enough rows to fill an MMA's 128: one launch of the tcgen05 kernel, a product per head along the grid's z
+        _check_t(load_tensor().llmk_gemm_tc_grouped(
+            _ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k), c_longlong(a.stride(0)), c_longlong(k),
+            c_longlong(out.stride(0)), c_int(_BF16), c_int(1), c_int(heads), c_int(k), c_longlong(n), c_void_p(0), c_void_p(0),
+            c_int(-1), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0), _stream()))
+        return
     _check(load().llmk_gemm_simt_batched(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                          c_longlong(a.stride(0)), c_longlong(k), c_longlong(out.stride(0)), c_int(heads),
                                          c_longlong(k), c_longlong(n * k), c_longlong(n), _ptr(gate),
@@ -209,9 +220,12 @@ def moe_tile() -> int:
     return int(load().llmk_moe_tile())
 
 
-def moe_max_tiles(n_pairs: int, experts: int) -> int:
+MOE_TC_TILE = 128       # slots per tile of the tensor-core grouped products (the MMA's 128 rows)
+
+
+def moe_max_tiles(n_pairs: int, experts: int, tile: int = 0) -> int:
     """Tiles that the grouped list of n_pairs (token, choice) pairs can take at most."""
-    return _ceil_div(n_pairs, moe_tile()) + min(experts, n_pairs)
+    return _ceil_div(n_pairs, tile or moe_tile()) + min(experts, n_pairs)
 
 
 def moe_route(h: torch.Tensor, w: torch.Tensor, bias, ids: torch.Tensor, weights: torch.Tensor, n_tokens: int, top: int) -> None:
@@ -226,13 +240,41 @@ def moe_route(h: torch.Tensor, w: torch.Tensor, bias, ids: torch.Tensor, weights
 
 
 def moe_group(ids: torch.Tensor, n_pairs: int, experts: int, meta: torch.Tensor, tile_expert: torch.Tensor,
-              slot_src: torch.Tensor, pair_slot: torch.Tensor, max_tiles: int) -> None:
-    """Sort the pairs by expert into tiles (see routed.cu); all int32 on the device."""
+              slot_src: torch.Tensor, pair_slot: torch.Tensor, max_tiles: int, tile: int = 0) -> None:
+    """Sort the pairs by expert into tiles of `tile` slots (see routed.cu); all int32 on the device."""
+    tile = tile or moe_tile()
     for t in (ids, meta, tile_expert, slot_src, pair_slot):
         assert t.dtype == torch.int32 and t.is_contiguous()
-    assert tile_expert.numel() >= max_tiles and slot_src.numel() >= max_tiles * moe_tile() and pair_slot.numel() >= n_pairs
+    assert tile_expert.numel() >= max_tiles and slot_src.numel() >= max_tiles * tile and pair_slot.numel() >= n_pairs
     _check(load().llmk_moe_group(_ptr(ids), c_int(n_pairs), c_int(experts), _ptr(meta), _ptr(tile_expert), _ptr(slot_src),
-                                 _ptr(pair_slot), c_int(max_tiles), _stream()))
+                                 _ptr(pair_slot), c_int(max_tiles), c_int(tile), _stream()))
+
+
+def moe_gather(out: torch.Tensor, x: torch.Tensor, slot_src, meta, div: int, tile: int, max_tiles: int) -> None:
+    """out[slot] = x[pair of the slot // div] for the slots of the tiles in use, zeros in padding slots."""
+    _rows_contig(x, "x")
+    assert out.is_contiguous() and out.dtype == x.dtype and out.shape[1] == x.shape[1] and out.shape[0] >= max_tiles * tile
+    _check(load().llmk_moe_gather(_ptr(out), _ptr(x), c_longlong(x.stride(0)), _ptr(slot_src), _ptr(meta), c_int(div),
+                                  c_int(x.shape[1]), c_int(tile), c_int(max_tiles), c_int(_kind(x.dtype)), _stream()))
+
+
+def moe_gemm_tc_available(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core grouped product takes these operands (bfloat16, rows of 16-byte multiples)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[2] % 8 == 0 and a.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def moe_gemm_tc(a: torch.Tensor, tile_expert, meta, w: torch.Tensor, out: torch.Tensor, max_tiles: int, act=None) -> None:
+    """out[slot] = act(a[slot] @ w[expert of the slot's tile].T) on the tensor cores: a [slots, K] in slot order
+    (tiles of 128 slots), w [experts, N, K], out bfloat16 or float32 [slots, N]."""
+    _rows_contig(a, "a"); _rows_contig(out, "out")
+    assert w.dim() == 3 and w.is_contiguous() and a.shape[1] == w.shape[2] and out.shape[1] == w.shape[1]
+    rows = max_tiles * MOE_TC_TILE
+    assert a.shape[0] >= rows and out.shape[0] >= rows
+    _check_t(load_tensor().llmk_gemm_tc_grouped(
+        _ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(w.shape[1]), c_int(w.shape[2]), c_longlong(a.stride(0)),
+        c_longlong(w.shape[2]), c_longlong(out.stride(0)), c_int(_kind(out.dtype)), c_int(2), c_int(w.shape[0]), c_int(0),
+        c_longlong(0), _ptr(tile_expert), _ptr(meta), c_int(ACTIVATIONS[act] if act else -1), c_void_p(0), c_longlong(0), _stream()))
 
 
 def moe_gemm(a: torch.Tensor, gather_div: int, slot_src, tile_expert, meta, w: torch.Tensor, out: torch.Tensor,

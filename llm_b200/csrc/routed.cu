@@ -81,7 +81,7 @@ route_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ 
 // One block.  counts -> padded offsets -> slots.  meta[0] = tiles in use.
 __global__ void __launch_bounds__(1024)
 group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ meta, int* __restrict__ tile_expert,
-             int* __restrict__ slot_src, int* __restrict__ pair_slot, int max_tiles) {
+             int* __restrict__ slot_src, int* __restrict__ pair_slot, int max_tiles, int TILE) {
   __shared__ int count[MAX_EXPERTS], offset[MAX_EXPERTS], cursor[MAX_EXPERTS];
   __shared__ int total_tiles;
   pdl_launch_dependents();
@@ -114,6 +114,26 @@ group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restr
     slot_src[slot] = i;
     pair_slot[i] = slot;
   }
+}
+
+// x_sorted[slot] = x[token of the slot's pair] (zeros in padding slots): the rows of the tokens in the
+// order of the slots, for a grouped product that reads its rows as whole tiles.
+template <typename T>
+__global__ void gather_rows_by_slot_kernel(T* __restrict__ out, const T* __restrict__ x, long long x_stride,
+                                           const int* __restrict__ slot_src, const int* __restrict__ meta, int div,
+                                           int cols, int tile) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x;
+  if (slot >= meta[0] * tile) return;
+  const int src = slot_src[slot];
+  T* dst = out + (size_t)slot * cols;
+  if (src < 0) {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = from_f32<T>(0.f);
+    return;
+  }
+  const T* row = x + (size_t)(src / div) * x_stride;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = row[c];
 }
 
 constexpr int BN = 64, BK = 16, TM = 4, TN = 4, THREADS = 256;
@@ -229,13 +249,29 @@ LLMK_API int llmk_moe_route(const void* h, long long h_stride, const void* w, co
 
 // ids [n_pairs] -> meta[0] (tiles in use), tile_expert [max_tiles], slot_src [max_tiles * 64] (the pair of
 // a slot, -1 for padding), pair_slot [n_pairs].  max_tiles >= ceil(n_pairs / 64) + min(experts, n_pairs).
+// tile: slots per tile (64 for the CUDA-core products of this file, 128 for the tensor-core ones).
 LLMK_API int llmk_moe_group(const int* ids, int n_pairs, int experts, int* meta, int* tile_expert, int* slot_src,
-                            int* pair_slot, int max_tiles, cudaStream_t stream) {
+                            int* pair_slot, int max_tiles, int tile, cudaStream_t stream) {
   if (n_pairs == 0) return 0;
   LLMK_REQUIRE(experts > 0 && experts <= MAX_EXPERTS, "moe_group: %d experts (1 to %d)", experts, MAX_EXPERTS);
+  LLMK_REQUIRE(tile > 0, "moe_group: tile %d", tile);
   launch_kernel(group_kernel, dim3(1), dim3(1024), 0, stream, ids, n_pairs, experts, meta, tile_expert, slot_src, pair_slot,
-                max_tiles);
+                max_tiles, tile);
   LLMK_LAUNCH_CHECK("moe_group");
+}
+
+// out [max_tiles * tile, cols] = the rows x[pair / div] in slot order, zeros in padding slots; slots of
+// tiles that are not in use are left alone.
+LLMK_API int llmk_moe_gather(void* out, const void* x, long long x_stride, const int* slot_src, const int* meta, int div,
+                             int cols, int tile, int max_tiles, int dtype, cudaStream_t stream) {
+  if (max_tiles == 0 || cols == 0) return 0;
+  LLMK_REQUIRE(div > 0 && tile > 0, "moe_gather: bad div %d or tile %d", div, tile);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(gather_rows_by_slot_kernel<T>, dim3((unsigned)(max_tiles * tile)), dim3(128), 0, stream, (T*)out, (const T*)x,
+                  x_stride, slot_src, meta, div, cols, tile);
+    LLMK_LAUNCH_CHECK("moe_gather");
+  });
 }
 
 // out_dtype: element kind of C (float32, or the input kind).  act: -1 none, else as llmk_act_rows.

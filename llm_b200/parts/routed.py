@@ -59,10 +59,13 @@ class RoutedFFN(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         T, ws, top, E = ctx.n_tokens, ctx.workspace, self.top, self.experts
-        pairs, tile = T * top, ops.moe_tile()
-        max_tiles = ops.moe_max_tiles(pairs, E)                       # of this step: a function of T alone
+        # bfloat16 runs the experts on the tensor cores (tiles of 128 slots, rows gathered into slot order
+        # first); float32, and shapes the tensor-core kernel refuses, on the CUDA cores (tiles of 64)
+        tensor = ops.moe_gemm_tc_available(x, self.w_up) and self.expert_size % 8 == 0
+        pairs, tile = T * top, (ops.MOE_TC_TILE if tensor else ops.moe_tile())
+        max_tiles = ops.moe_max_tiles(pairs, E, tile)                 # of this step: a function of T alone
         cap_pairs = ws.max_rows * top
-        cap_slots = ops.moe_max_tiles(cap_pairs, E) * tile            # of any step: the buffers' sizes
+        cap_slots = ops.moe_max_tiles(cap_pairs, E, tile) * tile      # of any step: the buffers' sizes
         i32, f32 = torch.int32, torch.float32
         ids, wts = ws.flat("moe_ids", cap_pairs, i32), ws.flat("moe_weights", cap_pairs, f32)
         pair_slot, meta = ws.flat("moe_pair_slot", cap_pairs, i32), ws.flat("moe_meta", 4, i32)
@@ -71,9 +74,15 @@ class RoutedFFN(Part):
         y = ws.flat("moe_y", cap_slots * self.hidden_size, f32).view(cap_slots, self.hidden_size)
 
         ops.moe_route(x, self.w_router, self.b_router, ids, wts, T, top)
-        ops.moe_group(ids, pairs, E, meta, tile_expert, slot_src, pair_slot, max_tiles)
-        ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, act, max_tiles, act=self.activation)
-        ops.moe_gemm(act, 0, slot_src, tile_expert, meta, self.w_down, y, max_tiles)
+        ops.moe_group(ids, pairs, E, meta, tile_expert, slot_src, pair_slot, max_tiles, tile)
+        if tensor:
+            rows = ws.flat("moe_rows", cap_slots * self.hidden_size, self.dtype).view(cap_slots, self.hidden_size)
+            ops.moe_gather(rows, x, slot_src, meta, top, tile, max_tiles)
+            ops.moe_gemm_tc(rows, tile_expert, meta, self.w_up, act, max_tiles, act=self.activation)
+            ops.moe_gemm_tc(act, tile_expert, meta, self.w_down, y, max_tiles)
+        else:
+            ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, act, max_tiles, act=self.activation)
+            ops.moe_gemm(act, 0, slot_src, tile_expert, meta, self.w_down, y, max_tiles)
         shared = self.shared.forward(x, ctx, tag="ffn_shared") if self.shared is not None else None
         out = ws.get("ffn_out", T, self.hidden_size, self.dtype)
         ops.moe_combine(out, y, pair_slot, wts, shared, T, top)

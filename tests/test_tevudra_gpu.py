@@ -80,7 +80,8 @@ def test_latent_norm_and_store(dtype, rank):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,n,k,rows", [(1, 8, 8, 1), (3, 24, 16, 5), (8, 96, 32, 70), (2, 20, 320, 9)])
+@pytest.mark.parametrize("heads,n,k,rows", [(1, 8, 8, 1), (3, 24, 16, 5), (8, 96, 32, 70), (2, 20, 320, 9), (4, 64, 128, 200),
+                                            (2, 320, 64, 130), (3, 40, 40, 100), (5, 300, 24, 257)])
 def test_per_head_products_with_gate(dtype, heads, n, k, rows):
     from llm_b200.csrc import ops
     g = torch.Generator().manual_seed(heads * 100 + n)
@@ -118,7 +119,7 @@ def _fake_ctx(rows, max_rows=64):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("experts,top,ff,shared,rows", [(4, 2, 40, 48, 13), (3, 3, 16, 0, 5), (8, 1, 64, 32, 1), (5, 2, 24, 72, 64),
-                                                        (2, 1, 8, 0, 150)])
+                                                        (2, 1, 8, 0, 150), (3, 2, 12, 0, 40), (2, 2, 264, 0, 140)])
 def test_routed_feed_forward_part(dtype, experts, top, ff, shared, rows):
     """The whole routed feed-forward (router, grouping, both grouped products, weighted sum, shared
     expert) as the part runs it; 150 rows of one or two experts fill more than one tile each."""
@@ -134,7 +135,7 @@ def test_routed_feed_forward_part(dtype, experts, top, ff, shared, rows):
     if shared:
         part.shared.bind(on_dev)
     h = bf(torch.randn(rows, W, generator=g))
-    ctx = _fake_ctx(rows, max_rows=160)
+    ctx = _fake_ctx(rows, max_rows=160)                 # (ff 12: not a multiple of 8, so bfloat16 too runs the CUDA-core products)
     out = part.forward(dev(h, dtype), ctx).clone()
     want = P.routed_ff(h, w["m.router"], w["m.router.b"], top, [(w[f"m.e{e}.up"], w[f"m.e{e}.down"]) for e in range(experts)],
                        (w["m.shared.up"], w["m.shared.down"]) if shared else None)
@@ -177,7 +178,7 @@ def plain_with_margin(cfg, w, toks):
 # In bfloat16 the router reads a rounded input, so a token whose last chosen logit lies this close to
 # the first one left out may be routed differently than in float64; such rows prove nothing and are
 # left out of the comparison (they are few, which is asserted).  Float32 compares every row.
-CLOSE_CALL = {"float32": 0.0, "bfloat16": 0.1}
+CLOSE_CALL = {"float32": 0.0, "bfloat16": 0.06}
 
 
 def compare(got, ref, dtype, what):
@@ -187,7 +188,7 @@ def compare(got, ref, dtype, what):
         margin = getattr(r, "margin", None)
         if margin is not None:
             unclear = margin < CLOSE_CALL[dtype]
-            assert int(unclear.sum()) <= max(2, len(unclear) // 4), f"{what}: too many close routing calls to compare {rid}"
+            assert int(unclear.sum()) <= max(2, len(unclear) // 3), f"{what}: too many close routing calls to compare {rid}"
             err_rows = torch.where(unclear, torch.zeros_like(err_rows), err_rows)
         bad = torch.nonzero(err_rows > TOL[dtype])
         assert bad.numel() == 0, (f"{what}: request {rid} first differs at position {int(bad[0])} "
