@@ -366,6 +366,127 @@ def decode_attention_sweep(args, peaks, torch, ops) -> int:
     return 0
 
 
+# ---- the Tevudra design beside the Llama decoder at equal layer sizes ------------------------
+def tevudra_config(width, layers, heads, dim, vdim, rank, dense_ff, experts, top, expert_ff, shared_ff, vocab=32000):
+    """Layers alternate: one that keeps its latents with a dense feed-forward, one that reads them with a routed one."""
+    ls = []
+    for i in range(layers):
+        mixer = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": rank, "scale": dim ** -0.5}
+        if i % 2:
+            mixer["kv_from"] = i - 1
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff}}
+        else:
+            mlp = {"kind": "dense", "ff": dense_ff}
+        ls.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Tevudra", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "layers": ls, "max_position": 4096}
+
+
+def llama_config(width, layers, heads, kv_heads, head_dim, ff, vocab=32000):
+    return dict(architectures=["LlamaForCausalLM"], hidden_size=width, intermediate_size=ff, num_hidden_layers=layers,
+                num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, vocab_size=vocab,
+                rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=4096, tie_word_embeddings=False)
+
+
+# name -> (Tevudra config, Llama config of the same width, depth, heads and about the same weights per layer)
+DESIGN_SIZES = {
+    "2048": (tevudra_config(2048, 8, 16, 128, 128, 128, 8192, 16, 4, 1024, 2048), llama_config(2048, 8, 16, 4, 128, 5632)),
+    "4096": (tevudra_config(4096, 4, 32, 128, 128, 128, 16384, 32, 4, 2048, 4096), llama_config(4096, 4, 32, 8, 128, 11008)),
+    "2048-rank512": (tevudra_config(2048, 4, 16, 128, 128, 512, 8192, 16, 4, 1024, 2048), llama_config(2048, 4, 16, 4, 128, 5632)),
+}
+
+
+def design_comparison(args, peaks) -> int:
+    """Prefill and decode throughput of Tevudra beside Llama at equal layer sizes (random weights, bfloat16), with
+    the device time of every kernel of one prompt step and one decode step.  One JSON line per size."""
+    import collections
+
+    import numpy as np
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from llm_b200.engine.engine import StepEntry
+    from llm_b200.engine.llm import LLM
+
+    rng = np.random.default_rng(3)
+    prompt_len, ctx_len, tokens = 2048, 512, args.prompt_tokens
+
+    def kernels_of(run):
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            run()
+            torch.cuda.synchronize()
+        agg = collections.OrderedDict()
+        for e in prof.events():
+            if e.device_type != torch.autograd.DeviceType.CUDA or not e.name or "Memcpy" in e.name or "Memset" in e.name:
+                continue
+            name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:60]
+            n, us = agg.get(name, (0, 0.0))
+            agg[name] = (n + 1, us + (e.time_range.end - e.time_range.start))
+        return {k: {"launches": n, "us": round(us, 1)} for k, (n, us) in agg.items()}
+
+    def measure(cfg):
+        vocab = cfg.get("vocab", cfg.get("vocab_size"))
+        llm = LLM(None, dtype="bfloat16", max_num_seqs=64, max_num_batched_tokens=max(tokens, 2048), max_seq_len=4096,
+                  eos_token_id=-1, kv_block_size=16, random_config=cfg, random_seed=7, random_on_device=True,
+                  num_kv_blocks=(64 * (ctx_len + 256) + 2 * tokens) // 16)
+        eng = llm.engine
+        toks = lambda n: [int(x) for x in rng.integers(0, vocab, size=n)]
+        out = {"weights_gb": round(eng.model.weight_bytes() / 1e9, 3)}
+
+        def one_prompt(k):
+            eng.step([StepEntry(f"p{k}", toks(tokens), [tokens - 1])])
+            eng.release(f"p{k}")
+        for k in range(3):
+            one_prompt(k)
+        reps = []
+        for k in range(3, 3 + max(3, min(args.steps, 8))):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); one_prompt(k); b.record()
+            torch.cuda.synchronize()
+            reps.append(a.elapsed_time(b))
+        ms = sorted(reps)[len(reps) // 2]
+        out["prefill"] = {"tokens": tokens, "ms": round(ms, 3), "tok_s": round(tokens / ms * 1e3)}
+        out["prefill_kernels"] = kernels_of(lambda: one_prompt(99))
+        out["decode"] = {}
+        for batch in (8, 64):
+            ids = [f"d{batch}_{i}" for i in range(batch)]
+            for i in range(0, batch, 4):
+                eng.step([StepEntry(r, toks(ctx_len), []) for r in ids[i:i + 4]])
+            steps, warm = 64, 8
+            feed = rng.integers(0, vocab, size=(warm + steps + 1, batch))
+            entries = lambda k: [StepEntry(r, [int(feed[k, j])], [0]) for j, r in enumerate(ids)]
+            for k in range(warm):
+                eng.step(entries(k))
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for k in range(warm, warm + steps):
+                eng.step(entries(k))
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            out["decode"][str(batch)] = {"ms_per_step": round(ms, 4), "tok_s": round(batch / ms * 1e3), "context": ctx_len + warm + steps}
+            if batch == 8:
+                out["decode_kernels"] = kernels_of(lambda: eng.step(entries(warm + steps)))
+            for r in ids:
+                eng.release(r)
+        del llm, eng
+        torch.cuda.empty_cache()
+        return out
+
+    sizes = [s for s in DESIGN_SIZES if not args.sizes or s in args.sizes.split(",")]
+    for name in sizes:
+        tev, lla = DESIGN_SIZES[name]
+        sampler = ClockSampler()
+        sampler.start()
+        res = {"mode": "tevudra", "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids",
+               "tevudra": measure(tev), "llama": measure(lla), "peaks": peaks}
+        res["clocks"] = sampler.stop()
+        print(json.dumps(res), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,11 +499,13 @@ def main() -> int:
     ap.add_argument("--no-shapes", action="store_true",
                     help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
     ap.add_argument("--mode", default="all",
-                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention"],
+                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention", "tevudra"],
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line); "
                          "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph; "
                          "decode_attention: the decode attention kernel alone over batches and context lengths "
-                         "(--batch with --ctx: that one case)")
+                         "(--batch with --ctx: that one case); "
+                         "tevudra: the Tevudra design beside Llama at equal layer sizes, prompt and decode, with every kernel's time")
+    ap.add_argument("--sizes", default="", help="tevudra: which of the sizes to run (comma-separated; default all)")
     ap.add_argument("--ctx", type=int, default=0, help="decode_attention: the context length of the one case to run")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="timeline_prefill: tokens of the prompt step")
     ap.add_argument("--heads", default="32,4,64", help="decode_attention: query heads, kv heads, head size")
@@ -405,6 +528,8 @@ def main() -> int:
     peaks = load_peaks()
     if args.mode == "decode_attention":
         return decode_attention_sweep(args, peaks, torch, ops)
+    if args.mode == "tevudra":
+        return design_comparison(args, peaks)
     cfg = dict(MODEL, num_hidden_layers=args.layers)
     if args.mode != "all":
         args.no_points = True

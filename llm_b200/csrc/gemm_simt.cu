@@ -112,6 +112,44 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, long long
   LLMK_LAUNCH_CHECK("gemm_simt");
 }
 
+// Few rows (a decode step): one warp per (product, output column).  The warp keeps its weight row in
+// registers (lane l holds k = l, l + 32, ...), dots every row of A with it and sums over the lanes in a
+// fixed order; the weights are read once, as a stream.  K up to 32 * GEMV_PER_LANE.
+constexpr int GEMV_PER_LANE = 16, GEMV_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+gemv_batched_kernel(const T* __restrict__ A, const T* __restrict__ W, T* __restrict__ C, int M, int N, int K, long long lda,
+                    long long ldw, long long ldc, long long a_batch, long long w_batch, long long c_batch,
+                    const T* __restrict__ gate, long long gate_stride) {
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * GEMV_WARPS + warp, z = blockIdx.y;
+  if (n >= N) return;
+  const T* w_row = W + (size_t)z * w_batch + (size_t)n * ldw;
+  float wr[GEMV_PER_LANE];
+#pragma unroll
+  for (int i = 0; i < GEMV_PER_LANE; ++i) {
+    const int k = lane + 32 * i;
+    wr[i] = k < K ? to_f32(w_row[k]) : 0.f;          // the weights do not depend on the kernel before
+  }
+  pdl_wait();
+  for (int m = 0; m < M; ++m) {
+    const T* a_row = A + (size_t)m * lda + (size_t)z * a_batch;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < GEMV_PER_LANE; ++i) {
+      const int k = lane + 32 * i;
+      if (k < K) s = fmaf(to_f32(a_row[k]), wr[i], s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+      if (gate) s *= 1.f / (1.f + expf(-to_f32(gate[(size_t)m * gate_stride + z])));
+      C[(size_t)m * ldc + (size_t)z * c_batch + n] = from_f32<T>(s);
+    }
+  }
+}
+
 }  // namespace
 
 // in_dtype: element kind of A and W; out_dtype: element kind of C (float32 or the same as in_dtype).
@@ -140,6 +178,14 @@ LLMK_API int llmk_gemm_simt_batched(const void* A, const void* W, void* C, int M
   LLMK_REQUIRE(K > 0 && lda >= K && ldw >= K && ldc >= N, "gemm_simt_batched: bad sizes M=%d N=%d K=%d", M, N, K);
   LLMK_REQUIRE((M + BM - 1) / BM <= 65535 && batches <= 65535, "gemm_simt_batched: M=%d or %d batches exceed the grid limit", M, batches);
   if (dtype == LLMK_F32) return launch<float, float>(A, W, C, M, N, K, lda, ldw, ldc, stream, batches, a_batch, w_batch, c_batch, gate, gate_stride);
+  if (dtype == LLMK_BF16 && M <= 24 && K <= 32 * GEMV_PER_LANE) {
+    // a decode step in bfloat16: the weights as a stream, one warp per output column (float32 keeps the tiled
+    // kernel at every row count, so that its sums never depend on how many rows a step brings)
+    using T = __nv_bfloat16;
+    launch_kernel(gemv_batched_kernel<T>, dim3((N + GEMV_WARPS - 1) / GEMV_WARPS, batches), dim3(GEMV_WARPS * 32), 0, stream,
+                  (const T*)A, (const T*)W, (T*)C, M, N, K, lda, ldw, ldc, a_batch, w_batch, c_batch, (const T*)gate, gate_stride);
+    LLMK_LAUNCH_CHECK("gemv_batched");
+  }
   if (dtype == LLMK_BF16)
     return launch<__nv_bfloat16, __nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, stream, batches, a_batch, w_batch, c_batch, gate, gate_stride);
   return llmk_fail(-1, "gemm_simt_batched: unsupported element kind %d", dtype);

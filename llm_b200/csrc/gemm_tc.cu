@@ -1155,6 +1155,8 @@ LLMK_API int llmk_gemm_tc_grouped(const void* A, const void* W, void* C, int M, 
   // the tile of weight rows: as wide as the product where that is at most 256 (in steps of 32), else 256 or 128
   int tile = (N + 31) / 32 * 32;
   if (tile > 256) tile = (N % 256 == 0 || N % 256 > 128) ? 256 : 128;
+  // few row tiles (a decode step's experts): narrower tiles put more CTAs on the weights' stream
+  if (mode == 2 && tile > 128 && (long long)(M / BP) * ((N + 255) / 256) < llmk_sm_count()) tile = 128;
   CUtensorMap mp, mq;
   if ((rc = get_map(&mp, A, M, mode == 1 ? (uint64_t)groups * a_k_step : (uint64_t)K, lda, M < BP ? M : BP))) return rc;
   if ((rc = get_map(&mq, W, (uint64_t)groups * N, K, ldw, tile))) return rc;

@@ -228,15 +228,25 @@ def moe_max_tiles(n_pairs: int, experts: int, tile: int = 0) -> int:
     return _ceil_div(n_pairs, tile or moe_tile()) + min(experts, n_pairs)
 
 
-def moe_route(h: torch.Tensor, w: torch.Tensor, bias, ids: torch.Tensor, weights: torch.Tensor, n_tokens: int, top: int) -> None:
-    """Router: float32 logits h @ w.T + bias, the `top` largest per token (ids, falling) and the softmax
-    over those alone (weights)."""
+def moe_route(h: torch.Tensor, w: torch.Tensor, bias, logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+              n_tokens: int, top: int) -> None:
+    """Router: logits = h @ w.T with float32 accumulation (the tensor-core product in bfloat16 where it takes the
+    shape, the CUDA-core product otherwise) into `logits` (float32 [>= n_tokens, experts]); plus bias, the `top`
+    largest per token (ids, falling) and the softmax over those alone (weights)."""
     _rows_contig(h, "h")
+    experts = w.shape[0]
     assert w.is_contiguous() and w.dtype == h.dtype and w.shape[1] == h.shape[1]
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape[1] == experts and logits.shape[0] >= n_tokens
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
-    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == w.shape[0])
-    _check(load().llmk_moe_route(_ptr(h), c_longlong(h.stride(0)), _ptr(w), _ptr(bias), _ptr(ids), _ptr(weights),
-                                 c_int(n_tokens), c_int(h.shape[1]), c_int(w.shape[0]), c_int(top), c_int(_kind(h.dtype)), _stream()))
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == experts)
+    if gemm_fast_available(h, w, logits, n_tokens):
+        z = gemm_fast(h, w, logits, n_tokens, allow_partial=True)
+    else:
+        gemm_simt(h, w, logits, n_tokens)
+        z = logits
+    d, parts, splits, stride = _split_args(z)
+    _check(load().llmk_moe_topk(d, parts, splits, stride, _ptr(bias), _ptr(ids), _ptr(weights), c_int(n_tokens),
+                                c_int(experts), c_int(top), _stream()))
 
 
 def moe_group(ids: torch.Tensor, n_pairs: int, experts: int, meta: torch.Tensor, tile_expert: torch.Tensor,

@@ -1,8 +1,9 @@
 // A routed feed-forward (mixture of experts): router, grouping of the tokens by expert, the
 // experts' two products over the groups, and the weighted sum.
 //
-//   route    z = h Wr^T + b in float32; the `top` largest z of a token (ties to the lower index);
-//            their weights are the softmax over those `top` values alone.
+//   route    z = h Wr^T + b with float32 accumulation (the engine's product kernels make h Wr^T); the
+//            `top` largest z of a token (ties to the lower index); their weights are the softmax
+//            over those `top` values alone.
 //   group    every (token, choice) pair gets a slot in a list that is sorted by expert, each
 //            expert's run padded to whole tiles of 64 slots, so that a tile of the products below
 //            belongs to one expert.  The launch sizes depend on the numbers of tokens, choices and
@@ -29,24 +30,18 @@ __device__ __forceinline__ float act_of(float z, int kind) {
   }
 }
 
-template <typename T>
+// One warp per token: its logits (a float32 tensor, or the unsummed partial results of the split-K
+// product that made them) plus the bias, then `top` rounds of arg-max over the warp.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-route_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ w, const float* __restrict__ bias,
-             int* __restrict__ ids, float* __restrict__ weights, int n_tokens, int width, int experts, int top) {
+topk_kernel(MaybePartial<float> z, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
+            int n_tokens, int experts, int top) {
   __shared__ float z_s[ROUTE_WARPS][MAX_EXPERTS];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
   if (t >= n_tokens) return;
-  const T* row = h + (size_t)t * h_stride;
-  for (int e = 0; e < experts; ++e) {
-    const T* we = w + (size_t)e * width;
-    float s = 0.f;
-    for (int c = lane; c < width; c += 32) s = fmaf(to_f32(row[c]), to_f32(we[c]), s);
-    s = warp_sum(s);
-    if (lane == 0) z_s[warp][e] = s + (bias ? bias[e] : 0.f);
-  }
+  for (int e = lane; e < experts; e += 32) z_s[warp][e] = z.at((size_t)t * experts + e) + (bias ? bias[e] : 0.f);
   __syncwarp();
   float z_max = 0.f, denom = 0.f;
   for (int j = 0; j < top; ++j) {
@@ -133,6 +128,12 @@ __global__ void gather_rows_by_slot_kernel(T* __restrict__ out, const T* __restr
     return;
   }
   const T* row = x + (size_t)(src / div) * x_stride;
+  constexpr int V = 16 / (int)sizeof(T);
+  if (cols % V == 0 && x_stride % V == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+    for (int c = threadIdx.x * V; c < cols; c += blockDim.x * V)
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(row + c);
+    return;
+  }
   for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = row[c];
 }
 
@@ -210,6 +211,33 @@ grouped_gemm_kernel(const T* __restrict__ A, long long lda, int gather_div, cons
   }
 }
 
+// four columns per thread where the rows allow 16-byte loads
+template <typename T>
+__global__ void combine4_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ pair_slot,
+                                const float* __restrict__ weights, MaybePartial<T> shared, int top, int width, size_t total4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = width / 4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / per_row;
+    const int c = (int)(i - t * per_row) * 4;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top; ++j) {
+      const int slot = pair_slot[t * top + j];
+      if (slot < 0) continue;
+      const float w = weights[t * top + j];
+      const float4 v = *reinterpret_cast<const float4*>(y + (size_t)slot * width + c);
+      s[0] = fmaf(w, v.x, s[0]); s[1] = fmaf(w, v.y, s[1]); s[2] = fmaf(w, v.z, s[2]); s[3] = fmaf(w, v.w, s[3]);
+    }
+    if (shared.present()) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) s[k] += shared.at(t * width + c + k);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) out[t * width + c + k] = from_f32<T>(s[k]);
+  }
+}
+
 template <typename T>
 __global__ void combine_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ pair_slot,
                                const float* __restrict__ weights, MaybePartial<T> shared, int top, int width, size_t total) {
@@ -232,19 +260,19 @@ __global__ void combine_kernel(T* __restrict__ out, const float* __restrict__ y,
 
 LLMK_API int llmk_moe_tile() { return TILE; }
 
-// h [n_tokens, h_stride] and w [experts, width] of the element kind, bias float32 [experts] or null;
-// ids int32 [n_tokens, top], weights float32 [n_tokens, top], both in the order of falling logits.
-LLMK_API int llmk_moe_route(const void* h, long long h_stride, const void* w, const float* bias, int* ids, float* weights,
-                            int n_tokens, int width, int experts, int top, int dtype, cudaStream_t stream) {
+// logits float32 [n_tokens, experts], or the partial results [splits][n_tokens][experts] of the product that
+// makes them; bias float32 [experts] or null; ids int32 [n_tokens, top], weights float32 [n_tokens, top], both in
+// the order of falling logits.
+LLMK_API int llmk_moe_topk(const float* logits, const float* partials, int splits, long long split_stride, const float* bias,
+                           int* ids, float* weights, int n_tokens, int experts, int top, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  LLMK_REQUIRE(experts > 0 && experts <= MAX_EXPERTS, "moe_route: %d experts (1 to %d)", experts, MAX_EXPERTS);
-  LLMK_REQUIRE(top > 0 && top <= experts, "moe_route: top %d of %d experts", top, experts);
-  return dispatch_dtype(dtype, [&](auto* tag) {
-    using T = LLMK_ELEM(tag);
-    launch_kernel(route_kernel<T>, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream,
-                  (const T*)h, h_stride, (const T*)w, bias, ids, weights, n_tokens, width, experts, top);
-    LLMK_LAUNCH_CHECK("moe_route");
-  });
+  LLMK_REQUIRE((logits != nullptr) != (partials != nullptr), "moe_topk: give logits or partials");
+  LLMK_REQUIRE(experts > 0 && experts <= MAX_EXPERTS, "moe_topk: %d experts (1 to %d)", experts, MAX_EXPERTS);
+  LLMK_REQUIRE(top > 0 && top <= experts, "moe_topk: top %d of %d experts", top, experts);
+  MaybePartial<float> z{logits, partials, splits, split_stride};
+  launch_kernel(topk_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream, z, bias, ids,
+                weights, n_tokens, experts, top);
+  LLMK_LAUNCH_CHECK("moe_topk");
 }
 
 // ids [n_pairs] -> meta[0] (tiles in use), tile_expert [max_tiles], slot_src [max_tiles * 64] (the pair of
@@ -306,7 +334,13 @@ LLMK_API int llmk_moe_combine(void* out, const float* y, const int* pair_slot, c
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> s{(const T*)shared, partials, splits, split_stride};
-    launch_kernel(combine_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, y, pair_slot, weights, s, top, width, total);
+    if (width % 4 == 0 && (uintptr_t)y % 16 == 0) {
+      size_t b4 = (total / 4 + 255) / 256;
+      if (b4 > (size_t)llmk_sm_count() * 16) b4 = (size_t)llmk_sm_count() * 16;
+      launch_kernel(combine4_kernel<T>, dim3((unsigned)b4), dim3(256), 0, stream, (T*)out, y, pair_slot, weights, s, top, width, total / 4);
+    } else {
+      launch_kernel(combine_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, y, pair_slot, weights, s, top, width, total);
+    }
     LLMK_LAUNCH_CHECK("moe_combine");
   });
 }

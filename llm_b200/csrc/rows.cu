@@ -270,6 +270,37 @@ __global__ void add_dyt_kernel(float* __restrict__ resid, MaybePartial<T> delta,
   }
 }
 
+// eight elements per thread (16-byte accesses) where the row length and the pointers allow it
+template <typename T>
+__global__ void add_dyt8_kernel(float* __restrict__ resid, MaybePartial<T> delta, const float* __restrict__ w,
+                                const float* __restrict__ b, float alpha, T* __restrict__ out, int hidden, size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const bool has_delta = delta.present();
+  const int per_row = hidden / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t at = i * 8;
+    const int c = (int)(i % per_row) * 8;
+    float v[8];
+    Vec8<float>::load(resid + at, v);
+    if (has_delta) {
+      float d[8];
+      delta.at8(at, d);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] += d[k];
+      Vec8<float>::store(resid + at, v);
+    }
+    if (out) {
+      float g[8], o[8];
+      Vec8<float>::load(w + c, g);
+      Vec8<float>::load(b + c, o);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = fmaf(tanhf(alpha * v[k]), g[k], o[k]);
+      Vec8<T>::store(out + at, v);
+    }
+  }
+}
+
 LLMK_API int llmk_add_dyt(float* resid, const void* delta, const float* partials, int splits, long long split_stride,
                           const float* w, const float* b, float alpha, void* out, int rows, int hidden, int dtype,
                           cudaStream_t stream) {
@@ -281,7 +312,15 @@ LLMK_API int llmk_add_dyt(float* resid, const void* delta, const float* partials
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> d{(const T*)delta, partials, splits, split_stride};
-    launch_kernel(add_dyt_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, resid, d, w, b, alpha, (T*)out, hidden, total);
+    const bool vec = hidden % 8 == 0 && d.vector_ok() && (uintptr_t)resid % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                     (uintptr_t)b % 16 == 0 && (uintptr_t)out % 16 == 0;
+    if (vec) {
+      size_t b8 = (total / 8 + 255) / 256;
+      if (b8 > (size_t)llmk_sm_count() * 16) b8 = (size_t)llmk_sm_count() * 16;
+      launch_kernel(add_dyt8_kernel<T>, dim3((unsigned)b8), dim3(256), 0, stream, resid, d, w, b, alpha, (T*)out, hidden, total / 8);
+    } else {
+      launch_kernel(add_dyt_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, resid, d, w, b, alpha, (T*)out, hidden, total);
+    }
     LLMK_LAUNCH_CHECK("add_dyt");
   });
 }
@@ -308,6 +347,19 @@ __global__ void act_rows_kernel(T* __restrict__ out, MaybePartial<T> in, int kin
     out[i] = from_f32<T>(apply_act(in.at(i), kind));
 }
 
+template <typename T>
+__global__ void act_rows8_kernel(T* __restrict__ out, MaybePartial<T> in, int kind, size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    float v[8];
+    in.at8(i * 8, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = apply_act(v[k], kind);
+    Vec8<T>::store(out + i * 8, v);
+  }
+}
+
 LLMK_API int llmk_act_rows(void* out, const void* in, const float* partials, int splits, long long split_stride,
                            long long total, int kind, int dtype, cudaStream_t stream) {
   if (total <= 0) return 0;
@@ -318,7 +370,13 @@ LLMK_API int llmk_act_rows(void* out, const void* in, const float* partials, int
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> x{(const T*)in, partials, splits, split_stride};
-    launch_kernel(act_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, x, kind, (size_t)total);
+    if (total % 8 == 0 && x.vector_ok() && (uintptr_t)out % 16 == 0) {
+      size_t b8 = ((size_t)total / 8 + 255) / 256;
+      if (b8 > (size_t)llmk_sm_count() * 32) b8 = (size_t)llmk_sm_count() * 32;
+      launch_kernel(act_rows8_kernel<T>, dim3((unsigned)b8), dim3(256), 0, stream, (T*)out, x, kind, (size_t)total / 8);
+    } else {
+      launch_kernel(act_rows_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, x, kind, (size_t)total);
+    }
     LLMK_LAUNCH_CHECK("act_rows");
   });
 }

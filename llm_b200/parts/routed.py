@@ -73,7 +73,8 @@ class RoutedFFN(Part):
         act = ws.flat("moe_act", cap_slots * self.expert_size, self.dtype).view(cap_slots, self.expert_size)
         y = ws.flat("moe_y", cap_slots * self.hidden_size, f32).view(cap_slots, self.hidden_size)
 
-        ops.moe_route(x, self.w_router, self.b_router, ids, wts, T, top)
+        logits = ws.get("moe_logits", T, E, f32)
+        ops.moe_route(x, self.w_router, self.b_router, logits, ids, wts, T, top)
         ops.moe_group(ids, pairs, E, meta, tile_expert, slot_src, pair_slot, max_tiles, tile)
         if tensor:
             rows = ws.flat("moe_rows", cap_slots * self.hidden_size, self.dtype).view(cap_slots, self.hidden_size)
