@@ -335,10 +335,11 @@ def decode_attention_sweep(args, peaks, torch, ops) -> int:
           f"peak {peaks['hbm_gbs']:.0f} GB/s ({peaks['source']})")
     for batch, ctx in cases:
         per_req = -(-ctx // page)
-        nbytes = batch * ctx * 4 * n_kv * hs
+        # --latent: one vector per token is key and value at once (a latent attention's cache), read once
+        nbytes = batch * ctx * (2 if args.latent else 4) * n_kv * hs
         sets = min(64, max(2, math.ceil(300e6 / nbytes)))
         k_pages = torch.randn(sets * batch * per_req, n_kv, page, hs, device=dev, dtype=torch.bfloat16)
-        v_pages = torch.randn_like(k_pages)
+        v_pages = k_pages if args.latent else torch.randn_like(k_pages)
         tables = torch.randperm(sets * batch * per_req, device=dev).to(torch.int32).view(sets, batch, per_req).contiguous()
         kv_lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
         q = torch.randn(batch, n_heads * hs, device=dev, dtype=torch.bfloat16)
@@ -505,6 +506,7 @@ def main() -> int:
                          "decode_attention: the decode attention kernel alone over batches and context lengths "
                          "(--batch with --ctx: that one case); "
                          "tevudra: the Tevudra design beside Llama at equal layer sizes, prompt and decode, with every kernel's time")
+    ap.add_argument("--latent", action="store_true", help="decode_attention: the key pages are the value pages too")
     ap.add_argument("--sizes", default="", help="tevudra: which of the sizes to run (comma-separated; default all)")
     ap.add_argument("--ctx", type=int, default=0, help="decode_attention: the context length of the one case to run")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="timeline_prefill: tokens of the prompt step")

@@ -159,6 +159,9 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
   const int k_begin = lo + split * chunk;
   const int k_end = min(pos + 1, k_begin + chunk);
   const int* table = block_table + (size_t)e * table_width;
+  // One vector per token that is key and value at once (the latents of a latent attention, whose pages are
+  // given as both): the tile of keys is also the tile of values, so only one of the two is requested.
+  const bool same_kv = !FUSED && k_pages == v_pages;
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;
   // the row of key k of this request and kv head in the pages.  The page size is a power of two
   // (the host sends other sizes to the CUDA-core kernel): a division per row of every tile would
@@ -187,7 +190,7 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
       const size_t row = row_of(kq);
       const int cs = (c & ~7) | ((c ^ kl) & 7);
       cp_async_16(dst + kl * (HS * 2) + cs * 16, k_pages + row + c * 8, valid);
-      cp_async_16(dst + V_BYTES + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
+      if (!same_kv) cp_async_16(dst + V_BYTES + kl * (HS * 2) + cs * 16, v_pages + row + c * 8, valid);
     }
     cp_async_commit();
   };
@@ -208,6 +211,7 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
     const int n_rows = min(ask_limit, max(0, k_end - k_begin - NST * 4 * TILE));
     for (int i = tid; i < n_rows * LINES * 2; i += THREADS) {
       const int which = i & 1, line = (i >> 1) % LINES, kp = k_begin + NST * 4 * TILE + (i >> 1) / LINES;
+      if (which && same_kv) continue;
       const size_t row = row_of(kp);
       const __nv_bfloat16* src = (which ? v_pages : k_pages) + row + line * 64;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
@@ -320,7 +324,7 @@ decode_attention_mma_kernel(__nv_bfloat16* __restrict__ out, long long out_strid
     }
     for (int j = 0; j < n_tiles; ++j) {
       const int t = t_first + j * 4 * TILE;
-      const uint32_t k_addr = w_addr + (j % NST) * 2 * V_BYTES, v_addr = k_addr + V_BYTES;
+      const uint32_t k_addr = w_addr + (j % NST) * 2 * V_BYTES, v_addr = same_kv ? k_addr : k_addr + V_BYTES;
       cp_async_wait_pending(min(n_tiles - 1 - j, NST - 1));          // tile j has landed; later ones may still fly
       __syncwarp();
       if (pos < t + TILE) {                                       // pos >= t: the range ends at pos

@@ -633,6 +633,7 @@ struct RopeStore {
   __nv_bfloat16* k_pages;
   __nv_bfloat16* v_pages;
   int n_heads, n_kv, head_dim, page_size;
+  int act_plus1;      // EPI_PLAIN only: 0 = store the product; else activation act_plus1 - 1 (see epilogue_act) on the accumulator
 };
 enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
 
@@ -798,6 +799,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
               tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              if (rs.act_plus1) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = epilogue_act(v[j], rs.act_plus1 - 1);
+              }
             }
           } else {
 #pragma unroll
@@ -1082,6 +1087,11 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
                           long long ldc, int out_dtype, int swap, int tile, int splits, int kblocks_per_split,
                           int cluster, int swiglu, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  // swiglu >= 2: not the gated activation but an element-wise one (swiglu - 2, see epilogue_act) applied to the
+  // product in the epilogue of the pair kernel
+  const int act = swiglu >= 2 ? swiglu - 2 : -1;
+  if (swiglu >= 2) swiglu = 0;
+  LLMK_REQUIRE(act < 0 || (cluster == 3 && act <= 3), "gemm_tc: an activation in the epilogue needs the pair kernel (and a kind 0..3)");
   if (swiglu) {
     LLMK_REQUIRE((cluster == 2 || cluster == 3) && !swap && splits == 1 && N % 2 == 0 && (N / 2) % 8 == 0,
                  "gemm_tc: silu(gate) * up in the epilogue needs the persistent kernel and an even N with N/2 a multiple of 8, got N=%d", N);
@@ -1114,8 +1124,10 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
       if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, EPI_SWIGLU>(mp, mq, C, ldc, M, N, K, tile, RopeStore{}, stream);
       return llmk_fail(-1, "gemm_tc: silu(gate) * up is written as bfloat16 only");
     }
-    if (out_dtype == LLMK_F32) return launch_pair<float, EPI_PLAIN>(mp, mq, C, ldc, M, N, K, tile, RopeStore{}, stream);
-    if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, EPI_PLAIN>(mp, mq, C, ldc, M, N, K, tile, RopeStore{}, stream);
+    RopeStore plain{};
+    plain.act_plus1 = act + 1;
+    if (out_dtype == LLMK_F32) return launch_pair<float, EPI_PLAIN>(mp, mq, C, ldc, M, N, K, tile, plain, stream);
+    if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, EPI_PLAIN>(mp, mq, C, ldc, M, N, K, tile, plain, stream);
     return llmk_fail(-1, "gemm_tc: unsupported output kind %d", out_dtype);
   }
   if (cluster == 2) {       // persistent kernel: normal mode, no split

@@ -838,6 +838,28 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) 
                                c_int(3 if PAIR_GEMM else 2), c_int(1), _stream()))
 
 
+def gemm_act_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> bool:
+    """Whether gemm_act takes this problem: bfloat16 throughout and more rows than the few-row modes serve
+    (there K is split over CTAs and the activation kernel sums the splits)."""
+    return PAIR_GEMM and rows > 128 and out.dtype == torch.bfloat16 and gemm_fast_available(a, w, out, rows)
+
+
+def gemm_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, act: str) -> None:
+    """out[:rows] = act(a[:rows] @ w.T) with the activation applied to the float32 accumulator in the epilogue of
+    the pair kernel, so the product itself never reaches memory."""
+    _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
+    n, k = w.shape
+    assert a.shape[1] == k and out.shape[1] == n
+    if not gemm_act_available(a, w, out, rows):
+        raise KernelError(f"gemm_act does not take {rows} rows of {a.dtype} -> {out.dtype}")
+    tile = 256 if n % 256 == 0 or n % 256 > 128 or n < 128 else 128
+    tile = min(tile, _ceil_div(n, 32) * 32)
+    _check_t(load_tensor().llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
+                               c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                               c_int(_BF16), c_int(0), c_int(tile), c_int(1), c_int(_ceil_div(k, 64)),
+                               c_int(3), c_int(2 + ACTIVATIONS[act]), _stream()))
+
+
 FUSE_PROMPT_ROPE = True
 
 

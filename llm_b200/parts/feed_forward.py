@@ -11,7 +11,7 @@ import torch
 
 from ..csrc import ops
 from .base import ParamInfo, Part, register_part
-from .linear import FUSE_PARTIALS, linear, linear_swiglu
+from .linear import FUSE_PARTIALS, linear, linear_act, linear_swiglu
 
 
 class SwiGLU(Part):
@@ -87,9 +87,10 @@ class ActMLP(Part):
 
     def forward(self, x: torch.Tensor, ctx, tag: str = "ffn") -> torch.Tensor:
         T, ws = ctx.n_tokens, ctx.workspace
-        up = linear(x, self.w_up, ws.get(tag + "_up", T, self.intermediate_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
         act = ws.get(tag + "_act", T, self.intermediate_size, self.dtype)
-        ops.act_rows(act, up, T, self.activation)
+        if not linear_act(x, self.w_up, act, T, self.activation):      # many rows: the activation in the product's epilogue
+            up = linear(x, self.w_up, ws.get(tag + "_up", T, self.intermediate_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+            ops.act_rows(act, up, T, self.activation)
         return linear(act, self.w_down, ws.get(tag + "_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 

@@ -55,3 +55,16 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows
         return False
     ops.gemm_swiglu(x, weight, out, rows)
     return True
+
+
+def linear_act(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, act: str) -> bool:
+    """out[:rows] = act(x @ weight.T) with the element-wise activation ("relu2", "gelu", "gelu_tanh", "silu")
+    applied in the product's epilogue.  Returns False, having done nothing, where that is not possible
+    (float32, shapes the tensor-core kernel refuses, or so few rows that the product splits its K
+    dimension): the caller then runs the product and the activation kernel."""
+    if rows == 0:
+        return True
+    if x.dtype != torch.bfloat16 or not ops.gemm_act_available(x, weight, out, rows):
+        return False
+    ops.gemm_act(x, weight, out, rows, act)
+    return True

@@ -59,7 +59,12 @@ CONFIG_S = {"architecture": "Tevudra", "width": 64, "vocab": 120, "norm": {"eps"
     _layer(_mixer(2, 16, 16, 48, 0.25), None),
 ]}
 
-CONFIGS = {"P": (CONFIG_P, 16), "Q": (CONFIG_Q, 16), "R": (CONFIG_R, 8), "S": (CONFIG_S, 16)}   # name -> (config, page size)
+# the same with a rank that the tensor-core attention kernels take, and more heads
+CONFIG_T = {"architecture": "Tevudra", "width": 64, "vocab": 120, "norm": {"eps": 1e-5}, "layers": [
+    _layer(_mixer(4, 16, 8, 64, 0.25), None),
+]}
+
+CONFIGS = {"P": (CONFIG_P, 16), "Q": (CONFIG_Q, 16), "R": (CONFIG_R, 8), "S": (CONFIG_S, 16), "T": (CONFIG_T, 16)}   # name -> (config, page size)
 
 
 def make_weights(cfg: dict, seed: int, peak: float = 1.5) -> dict:
