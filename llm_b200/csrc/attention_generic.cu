@@ -15,7 +15,7 @@
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_HEAD_DIM = 512;      // the kernel is built for head sizes up to 256 and up to 512
+constexpr int MAX_HEAD_DIM = 1024;     // the kernel is built for head sizes up to 256, up to 512 and up to 1024
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int head_dim);
@@ -153,7 +153,11 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
       launch_kernel(paged_attention_generic_kernel<T, 256>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
-    else      // the wide head of a latent attention (its rank)
+    else if (head_dim <= 512)      // the wide head of a latent attention (its rank)
+      launch_kernel(paged_attention_generic_kernel<T, 512>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
+          (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
+          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
+    else
       launch_kernel(paged_attention_generic_kernel<T, MAX_HEAD_DIM>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);

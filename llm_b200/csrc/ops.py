@@ -204,14 +204,14 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, h
 
 def latent_norm_store(x: torch.Tensor, gain: torch.Tensor, eps: float, slot_map: torch.Tensor, pages: torch.Tensor,
                       n_tokens: int) -> None:
-    """pages[slot_map[t]] = x[t] / sqrt(mean(x[t]^2) + eps) * gain for the first rank columns of x;
-    pages [pages, 1, page_size, rank]."""
+    """pages[slot_map[t]] = x[t] / sqrt(mean(x[t]^2) + eps) * gain for the first rank = len(gain) columns of x;
+    pages [pages, 1, page_size, width] with width >= rank (the rest of a row is written as zeros)."""
     _rows_contig(x, "x")
-    rank = pages.shape[3]
-    assert pages.is_contiguous() and pages.shape[1] == 1 and pages.dtype == x.dtype and x.shape[1] >= rank
-    assert gain.dtype == torch.float32 and gain.numel() == rank and slot_map.dtype == torch.int32
+    rank, width = gain.numel(), pages.shape[3]
+    assert pages.is_contiguous() and pages.shape[1] == 1 and pages.dtype == x.dtype and x.shape[1] >= rank and width >= rank
+    assert gain.dtype == torch.float32 and slot_map.dtype == torch.int32
     _check(load().llmk_latent_norm_store(_ptr(x), c_longlong(x.stride(0)), _ptr(gain), c_float(eps), _ptr(slot_map),
-                                         _ptr(pages), c_int(n_tokens), c_int(rank), c_int(_kind(x.dtype)), _stream()))
+                                         _ptr(pages), c_int(n_tokens), c_int(rank), c_int(width), c_int(_kind(x.dtype)), _stream()))
 
 
 @functools.lru_cache(maxsize=None)

@@ -37,14 +37,21 @@ class LatentAttention(Part):
         super().__init__(prefix, dtype, device)
         if min(hidden_size, num_heads, head_dim, value_dim, rank) <= 0:
             raise ValueError("latent attention: sizes must be positive")
-        if rank > 512:
-            raise ValueError(f"latent attention: rank {rank} exceeds 512, the widest head the attention kernels take")
+        if rank > 1024:
+            raise ValueError(f"latent attention: rank {rank} exceeds 1024, the widest head the attention kernels take")
         self.hidden_size, self.num_heads, self.head_dim, self.value_dim, self.rank = hidden_size, num_heads, head_dim, value_dim, rank
         self.scale, self.eps = float(scale), float(eps)
         self.gated = bool(gated)
         self.shares_cache = bool(shares_cache)      # reads another layer's latents: no down-projection of its own
         self.names = dict(_NAMES, **(names or {}))
         self.q_size = num_heads * head_dim
+        # The width of a cached row.  The tensor-core attention kernels (bfloat16) take heads of 64 or 128: a
+        # smaller rank is padded up to the next of the two with zeros (in the cache rows and in the two per-head
+        # maps), which changes no score and no output and costs cache, not correctness.  Other ranks, and
+        # float32, keep their width and run on the general kernels.
+        self.row_width = rank
+        if dtype == torch.bfloat16 and rank < 128 and rank != 64:
+            self.row_width = 64 if rank < 64 else 128
         self.w_in = None          # [q; down; gate] stacked: one product per step
         self.w_uk_t = None        # [heads, rank, dim]: the key map, transposed per head
         self.w_uv = None          # [heads, vdim, rank]
@@ -76,19 +83,23 @@ class LatentAttention(Part):
         H, D, V, R = self.num_heads, self.head_dim, self.value_dim, self.rank
         self.w_uk_t = n("up_k").view(H, D, R).transpose(1, 2).contiguous()
         self.w_uv = n("up_v").view(H, V, R).contiguous()
+        if self.row_width != R:
+            pad = self.row_width - R
+            self.w_uk_t = torch.nn.functional.pad(self.w_uk_t, (0, 0, 0, pad)).contiguous()      # [H, width, D]: zero rows
+            self.w_uv = torch.nn.functional.pad(self.w_uv, (0, pad)).contiguous()                # [H, V, width]: zero columns
         self.w_o = n("out").contiguous()
 
     def cache_need(self):
         if self.shares_cache:
             return None
-        return CacheNeed("full", 1, self.rank, None, values=False)
+        return CacheNeed("full", 1, self.row_width, None, values=False)
 
     def state_need(self):
         return None
 
     def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
         T, ws = ctx.n_tokens, ctx.workspace
-        H, R = self.num_heads, self.rank
+        H, R, RW = self.num_heads, self.rank, self.row_width
         proj = linear(x, self.w_in, ws.get("latent_in", T, self.w_in.shape[0], self.dtype), T)
         col = self.q_size
         pages = view.k_pages                        # [pages, 1, page_size, rank]; also the value pages
@@ -96,10 +107,10 @@ class LatentAttention(Part):
             ops.latent_norm_store(proj[:, col:col + R], self.gain, self.eps, view.group.slot_map, pages, T)
             col += R
         gate = proj[:, col:col + H] if self.gated else None
-        q_lat = ws.get("latent_q", T, H * R, self.dtype)
+        q_lat = ws.get("latent_q", T, H * RW, self.dtype)
         ops.gemm_heads(proj[:, :self.q_size], self.w_uk_t, q_lat, T, H)
-        o_lat = ws.get("latent_o", T, H * R, self.dtype)
-        ops.paged_attention(o_lat, q_lat, pages, pages, view.group, ctx, H, 1, R, 0, self.scale)
+        o_lat = ws.get("latent_o", T, H * RW, self.dtype)
+        ops.paged_attention(o_lat, q_lat, pages, pages, view.group, ctx, H, 1, RW, 0, self.scale)
         attn = ws.get("attn_out", T, H * self.value_dim, self.dtype)
         ops.gemm_heads(o_lat, self.w_uv, attn, T, H, gate=gate)
         return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)

@@ -74,23 +74,25 @@ def test_activation_in_the_products_epilogue(act, rows, n, k):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("rank", [8, 24, 96, 320])
-def test_latent_norm_and_store(dtype, rank):
-    """The cached vector against rms(x) * gain, written to shuffled places of the pages."""
+@pytest.mark.parametrize("rank,width", [(8, 8), (24, 64), (96, 96), (96, 128), (320, 320)])
+def test_latent_norm_and_store(dtype, rank, width):
+    """The cached vector against rms(x) * gain, written to shuffled places of the pages; rows wider than
+    the rank end in zeros whatever the page held before."""
     from llm_b200.csrc import ops
     g = torch.Generator().manual_seed(rank)
     T, page, pages = 21, 8, 6
     x = bf(torch.randn(T, rank + 5, generator=g) * 2)           # the projection is the first `rank` columns of wider rows
     gain, eps = 1 + 0.3 * torch.randn(rank, generator=g), 1e-3
     slots = torch.randperm(page * pages, generator=g)[:T].to(torch.int32)
-    store = torch.zeros(pages, 1, page, rank, device="cuda", dtype=DT[dtype])
+    store = torch.full((pages, 1, page, width), 7.0, device="cuda", dtype=DT[dtype])
     ops.latent_norm_store(dev(x, dtype)[:, :rank], dev(gain), eps, slots.cuda(), store, T)
     want = P.rms(x[:, :rank], gain, eps)
-    got = store.view(-1, rank)[slots.long().cuda()]
-    assert max_err(got, want) < KTOL[dtype]
+    got = store.view(-1, width)[slots.long().cuda()]
+    assert max_err(got[:, :rank], want) < KTOL[dtype]
+    assert width == rank or float(got[:, rank:].abs().max()) == 0.0
     untouched = torch.ones(page * pages, dtype=torch.bool)
     untouched[slots.long()] = False
-    assert float(store.view(-1, rank)[untouched.cuda()].abs().max()) == 0.0
+    assert float((store.view(-1, width)[untouched.cuda()] - 7.0).abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
