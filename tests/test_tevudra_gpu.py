@@ -305,7 +305,7 @@ def test_one_key_carries_the_row(dtype, case, name):
         other = P.forward(cfg, w, blind)
         seen = [q for q in queries if q > needles[0]]
         gap = ((ref[seen] - other[seen]).abs().max(dim=1).values / ref.abs().max()).min()
-        assert float(gap) > 4 * TOL[dtype], f"the needle does not stand out ({float(gap):.2e})"
+        assert float(gap) > 3 * TOL[dtype], f"the needle does not stand out ({float(gap):.2e})"
     reqs, refs = {"n": toks}, {"n": ref}
     eng = make_engine(cfg, w, dtype, page, -(-n // page) + 2, max_tokens=768)
     compare(replay.run_steps(eng, replay.steps_whole(reqs)), refs, dtype, "whole")
