@@ -162,7 +162,8 @@ def test_routed_feed_forward_part(dtype, experts, top, ff, shared, rows):
 
 
 # ---- whole models, every way of cutting the work --------------------------------------------
-LENGTHS = {"P": [1, 5, 33, 70, 129], "Q": [2, 47, 64, 150, 260], "R": [3, 40, 17, 90], "S": [1, 16, 31, 100], "T": [1, 130, 31, 257]}
+LENGTHS = {"P": [1, 5, 33, 70, 129], "Q": [2, 47, 64, 150, 260], "R": [3, 40, 17, 90], "S": [1, 16, 31, 100], "T": [1, 130, 31, 257],
+           "U": [2, 33, 64, 95, 140]}
 
 
 @pytest.fixture(scope="module")
@@ -215,7 +216,7 @@ def compare(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "T"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "T", "U"])
 def test_every_cut_matches_plain(models, name, dtype):
     cfg, page, w, reqs, ref = models(name)
     longest = max(len(t) for t in reqs.values())

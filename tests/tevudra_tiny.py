@@ -64,7 +64,15 @@ CONFIG_T = {"architecture": "Tevudra", "width": 64, "vocab": 120, "norm": {"eps"
     _layer(_mixer(4, 16, 8, 64, 0.25), None),
 ]}
 
-CONFIGS = {"P": (CONFIG_P, 16), "Q": (CONFIG_Q, 16), "R": (CONFIG_R, 8), "S": (CONFIG_S, 16), "T": (CONFIG_T, 16)}   # name -> (config, page size)
+# U: nothing on a grid of 8 or 16 (width, vocabulary, head sizes, ranks, feed-forward sizes), so that bfloat16 too
+# runs the any-size kernels; a rank above 128 that is not a multiple of 16
+CONFIG_U = {"architecture": "Tevudra", "width": 100, "vocab": 97, "norm": {"eps": 3e-6}, "layers": [
+    _layer(_mixer(3, 10, 6, 20, 0.3), _moe(5, 2, 14, shared=22)),
+    _layer(_mixer(5, 6, 14, 20, 0.45, kv_from=0), _dense(30)),
+    _layer(_mixer(2, 12, 10, 136, 0.28), _moe(7, 3, 10)),
+]}
+
+CONFIGS = {"U": (CONFIG_U, 32), "P": (CONFIG_P, 16), "Q": (CONFIG_Q, 16), "R": (CONFIG_R, 8), "S": (CONFIG_S, 16), "T": (CONFIG_T, 16)}   # name -> (config, page size)
 
 
 def make_weights(cfg: dict, seed: int, peak: float = 1.5) -> dict:
