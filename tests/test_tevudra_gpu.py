@@ -163,7 +163,7 @@ def test_routed_feed_forward_part(dtype, experts, top, ff, shared, rows):
 
 # ---- whole models, every way of cutting the work --------------------------------------------
 LENGTHS = {"P": [1, 5, 33, 70, 129], "Q": [2, 47, 64, 150, 260], "R": [3, 40, 17, 90], "S": [1, 16, 31, 100], "T": [1, 130, 31, 257],
-           "U": [2, 33, 64, 95, 140]}
+           "U": [2, 33, 64, 95, 140], "V": [1, 18, 77, 150]}
 
 
 @pytest.fixture(scope="module")
@@ -216,7 +216,7 @@ def compare(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "T", "U"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "T", "U", "V"])
 def test_every_cut_matches_plain(models, name, dtype):
     cfg, page, w, reqs, ref = models(name)
     longest = max(len(t) for t in reqs.values())

@@ -72,7 +72,14 @@ CONFIG_U = {"architecture": "Tevudra", "width": 100, "vocab": 97, "norm": {"eps"
     _layer(_mixer(2, 12, 10, 136, 0.28), _moe(7, 3, 10)),
 ]}
 
-CONFIGS = {"U": (CONFIG_U, 32), "P": (CONFIG_P, 16), "Q": (CONFIG_Q, 16), "R": (CONFIG_R, 8), "S": (CONFIG_S, 16), "T": (CONFIG_T, 16)}   # name -> (config, page size)
+# V: ranks above 128 on the 16-grid, which in bfloat16 decode on the CUDA-core split-key kernel
+CONFIG_V = {"architecture": "Tevudra", "width": 80, "vocab": 130, "norm": {"eps": 1e-5}, "layers": [
+    _layer(_mixer(2, 24, 16, 160, 0.2), _dense(48)),
+    _layer(_mixer(4, 16, 16, 256, 0.25), _moe(4, 2, 24, shared=16)),
+    _layer(_mixer(3, 8, 24, 160, 0.3, kv_from=0), None),
+]}
+
+CONFIGS = {"V": (CONFIG_V, 16), "U": (CONFIG_U, 32), "P": (CONFIG_P, 16), "Q": (CONFIG_Q, 16), "R": (CONFIG_R, 8), "S": (CONFIG_S, 16), "T": (CONFIG_T, 16)}   # name -> (config, page size)
 
 
 def make_weights(cfg: dict, seed: int, peak: float = 1.5) -> dict:
