@@ -446,7 +446,7 @@ template <typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                           TOut* __restrict__ C, long long ldc, int M, int N, int K, int tile_q,
-                          int* __restrict__ err_flag) {
+                          int* __restrict__ err_flag, const Grouping grp) {
   constexpr int BNQ = 256;
   constexpr int STAGES = stages_for(BNQ);
   constexpr int Q_STAGE_BYTES = q_stage_bytes(BNQ);
@@ -466,8 +466,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int inter = N / 2;                                 // SWIGLU: gate rows, and output columns
-  const int m_tiles = (M + BP - 1) / BP, n_tiles = SWIGLU ? (inter + 127) / 128 : (N + tile_q - 1) / tile_q;
-  const int total_tiles = m_tiles * n_tiles;
+  int m_tiles = (M + BP - 1) / BP;
+  const int n_tiles = SWIGLU ? (inter + 127) / 128 : (N + tile_q - 1) / tile_q;
   const int nkb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -490,6 +490,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
   const uint32_t tmem_base = *tmem_slot;
 
   pdl_launch_dependents();
+  if (grp.mode == 2) {
+    // row tiles by group (see Grouping): how many are in use is what the kernel before this one wrote, and
+    // every role walks over the same tiles, so every thread waits for it here
+    pdl_wait();
+    m_tiles = min(m_tiles, *grp.n_tiles);
+  }
+  const int total_tiles = m_tiles * n_tiles;
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer ----
@@ -498,7 +505,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
       int it = 0;                                             // k-blocks issued so far, over all tiles
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int p0 = tile_row0((tile % m_tiles) * BP, M);
-        const int q0 = SWIGLU ? (tile / m_tiles) * 128 : tile_col0((tile / m_tiles) * tile_q, tile_q, N);
+        const int w_base = grp.mode == 2 ? grp.tile_group[tile % m_tiles] * grp.w_row_step : 0;      // the group's rows of W
+        const int q0 = w_base + (SWIGLU ? (tile / m_tiles) * 128 : tile_col0((tile / m_tiles) * tile_q, tile_q, N));
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1);
@@ -573,6 +581,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if (grp.act >= 0) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = epilogue_act(v[j], grp.act);
+            }
           }
         } else {
 #pragma unroll
@@ -969,7 +981,7 @@ int launch_cfg(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long 
 
 template <typename TOut, bool SWIGLU>
 int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, long long ldc, int M, int N, int K,
-                      int tile_q, cudaStream_t stream) {
+                      int tile_q, cudaStream_t stream, const Grouping grp = Grouping{0, 0, 0, nullptr, nullptr, -1, nullptr, 0}) {
   auto kern = gemm_tc_persistent_kernel<TOut, SWIGLU>;
   constexpr int smem = smem_bytes_for(256);
   static bool configured = false;
@@ -980,7 +992,7 @@ int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, void* C, lon
   }
   const int tiles = ((M + BP - 1) / BP) * (SWIGLU ? (N / 2 + 127) / 128 : (N + tile_q - 1) / tile_q);
   launch_kernel(kern, dim3(tiles < llmk_sm_count() ? tiles : llmk_sm_count()), dim3(THREADS), (size_t)smem, stream, mp, mq, (TOut*)C, ldc, M, N, K,
-                tile_q, g_err_flag);
+                tile_q, g_err_flag, grp);
   LLMK_LAUNCH_CHECK("gemm_tc_persistent");
 }
 
@@ -1173,6 +1185,13 @@ LLMK_API int llmk_gemm_tc_grouped(const void* A, const void* W, void* C, int M, 
   if ((rc = get_map(&mp, A, M, mode == 1 ? (uint64_t)groups * a_k_step : (uint64_t)K, lda, M < BP ? M : BP))) return rc;
   if ((rc = get_map(&mq, W, (uint64_t)groups * N, K, ldw, tile))) return rc;
   const Grouping grp{mode, a_k_step, N, tile_group, n_tiles, act, (const __nv_bfloat16*)gate, gate_stride};
+  if (mode == 2 && (long long)(M / BP) * ((N + tile - 1) / tile) > llmk_sm_count()) {
+    // more tiles than SMs (a prompt's experts): persistent CTAs with two accumulators, so that a tile's
+    // epilogue runs under the next tile's products and no partial wave is left at the end
+    if (out_dtype == LLMK_F32) return launch_persistent<float, false>(mp, mq, C, ldc, M, N, K, tile, stream, grp);
+    if (out_dtype == LLMK_BF16) return launch_persistent<__nv_bfloat16, false>(mp, mq, C, ldc, M, N, K, tile, stream, grp);
+    return llmk_fail(-1, "gemm_tc_grouped: unsupported output kind %d", out_dtype);
+  }
   const int splits = mode == 1 ? groups : 1;            // the grid's z: one product each
   const int kb = (K + BK - 1) / BK;
   const long long step = mode == 1 ? c_step : 0;

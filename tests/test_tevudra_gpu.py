@@ -136,13 +136,13 @@ def _fake_ctx(rows, max_rows=64):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("experts,top,ff,shared,rows", [(4, 2, 40, 48, 13), (3, 3, 16, 0, 5), (8, 1, 64, 32, 1), (5, 2, 24, 72, 64),
-                                                        (2, 1, 8, 0, 150), (3, 2, 12, 0, 40), (2, 2, 264, 0, 140)])
+                                                        (2, 1, 8, 0, 150), (3, 2, 12, 0, 40), (2, 2, 264, 0, 140), (4, 4, 264, 0, 2500)])
 def test_routed_feed_forward_part(dtype, experts, top, ff, shared, rows):
     """The whole routed feed-forward (router, grouping, both grouped products, weighted sum, shared
     expert) as the part runs it; 150 rows of one or two experts fill more than one tile each."""
     from llm_b200.parts.routed import RoutedFFN
     g = torch.Generator().manual_seed(experts * 7 + rows)
-    W = 32
+    W = 32 if rows < 1000 else 320      # the large case has more tiles than SMs in both grouped products (persistent CTAs)
     part = RoutedFFN(W, experts, top, ff, "gelu", True, shared, prefix="m", dtype=DT[dtype], device=torch.device("cuda"))
     w = {}
     for name, info in list(part.parameters().items()) + (list(part.shared.parameters().items()) if shared else []):
@@ -152,7 +152,7 @@ def test_routed_feed_forward_part(dtype, experts, top, ff, shared, rows):
     if shared:
         part.shared.bind(on_dev)
     h = bf(torch.randn(rows, W, generator=g))
-    ctx = _fake_ctx(rows, max_rows=160)                 # (ff 12: not a multiple of 8, so bfloat16 too runs the CUDA-core products)
+    ctx = _fake_ctx(rows, max_rows=max(160, rows))                 # (ff 12: not a multiple of 8, so bfloat16 too runs the CUDA-core products)
     out = part.forward(dev(h, dtype), ctx).clone()
     want = P.routed_ff(h, w["m.router"], w["m.router.b"], top, [(w[f"m.e{e}.up"], w[f"m.e{e}.down"]) for e in range(experts)],
                        (w["m.shared.up"], w["m.shared.down"]) if shared else None)
