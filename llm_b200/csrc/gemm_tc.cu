@@ -1163,11 +1163,12 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
 // mode 1 (by_z): A [M, groups * a_k_step] (K <= a_k_step columns of a group are used), W [groups * N, K],
 //   C [M, >= groups * c_step] (group g writes N columns from g * c_step); gate [M, gate_stride] or null.
 // mode 2 (by_tile): A [M, K] with M a multiple of 128 (rows sorted by group, runs padded to whole tiles),
-//   W [groups * N, K], C [M, ldc]; tile_group [M / 128] and n_tiles [1] on the device.
+//   W [groups * N, K], C [M, ldc]; tile_group [M / 128] and n_tiles [1] on the device.  persistent != 0: more tiles
+//   than SMs run on the persistent kernel (one CTA per SM, two accumulators).
 LLMK_API int llmk_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
                                   long long ldc, int out_dtype, int mode, int groups, int a_k_step, long long c_step,
                                   const int* tile_group, const int* n_tiles, int act, const void* gate,
-                                  long long gate_stride, cudaStream_t stream) {
+                                  long long gate_stride, int persistent, cudaStream_t stream) {
   if (M == 0 || N == 0 || groups == 0) return 0;
   LLMK_REQUIRE(mode == 1 || mode == 2, "gemm_tc_grouped: mode %d (1 = by product, 2 = by row tile)", mode);
   LLMK_REQUIRE(llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw), "gemm_tc_grouped: K=%d and the row pitches must be multiples of 8 and the bases 16-byte aligned", K);
@@ -1185,7 +1186,7 @@ LLMK_API int llmk_gemm_tc_grouped(const void* A, const void* W, void* C, int M, 
   if ((rc = get_map(&mp, A, M, mode == 1 ? (uint64_t)groups * a_k_step : (uint64_t)K, lda, M < BP ? M : BP))) return rc;
   if ((rc = get_map(&mq, W, (uint64_t)groups * N, K, ldw, tile))) return rc;
   const Grouping grp{mode, a_k_step, N, tile_group, n_tiles, act, (const __nv_bfloat16*)gate, gate_stride};
-  if (mode == 2 && (long long)(M / BP) * ((N + tile - 1) / tile) > llmk_sm_count()) {
+  if (persistent && mode == 2 && (long long)(M / BP) * ((N + tile - 1) / tile) > llmk_sm_count()) {
     // more tiles than SMs (a prompt's experts): persistent CTAs with two accumulators, so that a tile's
     // epilogue runs under the next tile's products and no partial wave is left at the end
     if (out_dtype == LLMK_F32) return launch_persistent<float, false>(mp, mq, C, ldc, M, N, K, tile, stream, grp);

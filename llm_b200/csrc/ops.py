@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -194,7 +195,7 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, h
         _check_t(load_tensor().llmk_gemm_tc_grouped(
             _ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k), c_longlong(a.stride(0)), c_longlong(k),
             c_longlong(out.stride(0)), c_int(_BF16), c_int(1), c_int(heads), c_int(k), c_longlong(n), c_void_p(0), c_void_p(0),
-            c_int(-1), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0), _stream()))
+            c_int(-1), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0), c_int(0), _stream()))
         return
     _check(load().llmk_gemm_simt_batched(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                          c_longlong(a.stride(0)), c_longlong(k), c_longlong(out.stride(0)), c_int(heads),
@@ -220,6 +221,7 @@ def moe_tile() -> int:
     return int(load().llmk_moe_tile())
 
 
+GROUPED_PERSISTENT = os.environ.get("LLM_B200_GROUPED_PERSISTENT", "1") != "0"      # see moe_gemm_tc
 MOE_TC_TILE = 128       # slots per tile of the tensor-core grouped products (the MMA's 128 rows)
 
 
@@ -284,7 +286,8 @@ def moe_gemm_tc(a: torch.Tensor, tile_expert, meta, w: torch.Tensor, out: torch.
     _check_t(load_tensor().llmk_gemm_tc_grouped(
         _ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(w.shape[1]), c_int(w.shape[2]), c_longlong(a.stride(0)),
         c_longlong(w.shape[2]), c_longlong(out.stride(0)), c_int(_kind(out.dtype)), c_int(2), c_int(w.shape[0]), c_int(0),
-        c_longlong(0), _ptr(tile_expert), _ptr(meta), c_int(ACTIVATIONS[act] if act else -1), c_void_p(0), c_longlong(0), _stream()))
+        c_longlong(0), _ptr(tile_expert), _ptr(meta), c_int(ACTIVATIONS[act] if act else -1), c_void_p(0), c_longlong(0),
+        c_int(int(GROUPED_PERSISTENT)), _stream()))
 
 
 def moe_gemm(a: torch.Tensor, gather_div: int, slot_src, tile_expert, meta, w: torch.Tensor, out: torch.Tensor,
