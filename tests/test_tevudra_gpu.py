@@ -379,3 +379,52 @@ def test_trace_replay_of_a_folder(models, tmp_path):
             assert max_err(got[r:r + k], ref[rid][at[rid]:at[rid] + k]) < 1e-4
             at[rid] += k
             r += k
+
+
+# ---- seeded random configurations -----------------------------------------------------------
+def _random_config(seed):
+    """Sizes, constants and layer order drawn from a seed: widths and ranks on and off the grids of 8 and 16,
+    any mix of own and borrowed latents, of dense, routed and absent feed-forwards."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([40, 56, 72, 88, 100, 128, 136])
+    layers, owners = [], []
+    for i in range(rng.randint(2, 5)):
+        heads, dim, vdim = rng.randint(1, 6), rng.choice([4, 8, 10, 16, 24, 40]), rng.choice([4, 8, 12, 16, 32])
+        if owners and rng.random() < 0.45:
+            src = rng.choice(owners)
+            mixer = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": layers[src]["mixer"]["kv_rank"],
+                     "scale": rng.uniform(0.1, 0.5), "kv_from": src}
+        else:
+            owners.append(i)
+            mixer = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": rng.choice([8, 12, 32, 48, 64, 80, 100, 128, 144, 192]),
+                     "scale": rng.uniform(0.1, 0.5)}
+        kind = rng.choice(["dense", "moe", "moe", None])
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": rng.choice([24, 50, 64, 96])}
+        elif kind == "moe":
+            experts = rng.randint(1, 9)
+            mlp = {"kind": "moe", "expert": {"ff": rng.choice([8, 12, 24, 40])},
+                   "router": {"experts": experts, "top": rng.randint(1, experts)}}
+            if rng.random() < 0.6:
+                mlp["shared"] = {"ff": rng.choice([8, 20, 32])}
+        else:
+            mlp = None
+        layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Tevudra", "width": width, "vocab": rng.choice([61, 128, 200, 333]),
+            "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])}, "layers": layers}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(8))
+def test_seeded_random_configurations(seed, dtype):
+    cfg = _random_config(1000 + seed)
+    w = make_weights(cfg, seed=seed, peak=1.0)
+    page = [8, 16, 32][seed % 3]
+    reqs = {f"r{i}": random_tokens(n, cfg["vocab"], 40 + i) for i, n in enumerate([3, 45, 70, 131])}
+    ref = {rid: plain_with_margin(cfg, w, toks) for rid, toks in reqs.items()}
+    eng = make_engine(cfg, w, dtype, page, sum(-(-len(t) // page) for t in reqs.values()) + 1)
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, f"seed {seed} whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs, tail=20)), ref, dtype, f"seed {seed} tail decode")
+    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, f"seed {seed} mixed")
+    eng.cache.check()
