@@ -41,12 +41,15 @@ class GroupSpec:
     page_size: int
     num_pages: int
     window: Optional[int] = None   # tokens visible to a query, itself included
+    keep_first: int = 0            # window groups: a request's first tokens that stay visible, so their pages are never given back
 
     def __post_init__(self):
         if self.kind not in ("full", "window"):
             raise CacheError(f"unknown cache group kind '{self.kind}'")
         if self.kind == "window" and not (self.window and self.window > 0):
             raise CacheError("a window group needs a positive window")
+        if self.keep_first < 0 or (self.keep_first and self.kind != "window"):
+            raise CacheError("keep_first belongs to a window group and is not negative")
         if self.page_size <= 0 or self.num_pages < 0:
             raise CacheError("page_size must be positive and num_pages non-negative")
 
@@ -79,7 +82,8 @@ class CacheManager:
         arr = lambda vals: (ctypes.c_int * max(n, 1))(*vals)
         self._pool = lib.llmh_pool_create(
             n, arr([_KINDS[g.kind] for g in groups]), arr([g.page_size for g in groups]),
-            arr([g.num_pages for g in groups]), arr([g.window or 0 for g in groups]), max_requests, max_seq_len)
+            arr([g.num_pages for g in groups]), arr([g.window or 0 for g in groups]),
+            arr([g.keep_first or 0 for g in groups]), max_requests, max_seq_len)
         if not self._pool:
             raise CacheError("the page pool refused these groups")
         self._pool = ctypes.c_void_p(self._pool)

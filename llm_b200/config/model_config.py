@@ -214,6 +214,104 @@ class TevudraConfig:
         return self.max_position
 
 
+def _moe_of(ff, where: str):
+    """{kind: moe, expert: {ff}, router: {experts, top}} -> a flat dict, validated."""
+    if not isinstance(ff, dict):
+        raise ConfigError(f"config.json: {where}.mlp must be an object or null")
+    if _take(ff, "kind", str) != "moe":
+        raise ConfigError(f"config.json: {where}.mlp.kind '{ff['kind']}' is not 'moe'")
+    router = _take(ff, "router", dict)
+    mlp = {"kind": "moe", "ff": _take(_take(ff, "expert", dict), "ff", int),
+           "experts": _take(router, "experts", int), "top": _take(router, "top", int)}
+    if not (0 < mlp["top"] <= mlp["experts"]) or mlp["ff"] <= 0:
+        raise ConfigError(f"config.json: {where}.mlp: top {mlp['top']} of {mlp['experts']} experts of size {mlp['ff']}")
+    return mlp
+
+
+@dataclass(frozen=True)
+class FopivikConfig:
+    """config.json of a Fopivik folder: a decoder whose layers are listed one by one, part of which may run
+    several times in a row.
+
+    Top level: `architecture`, `width`, `vocab`, `norm.eps`, `residual_mult`, `logit_softcap`, `layers`, `loop`
+    ({start, stop, times}: layers start..stop-1 run `times` times with the same weights; absent or null: once).
+    A layer gives `type` (its mixer: "attention" or "gla"), `mixer` and `mlp` (a mixture of experts
+    {kind: moe, expert: {ff}, router: {experts, top}}, or null).  attention: heads, kv_heads, dim, vdim, scale,
+    softcap, mask {size, keep_first}, rot {dims, base, scaling {factor, low, high, original} or absent}.
+    gla: heads, dim, vdim, tau.  The design has no length limit of its own: max_position (optional) bounds
+    what the engine sizes its tables for."""
+
+    architecture: str
+    width: int
+    vocab: int
+    norm_eps: float
+    residual_mult: float
+    logit_softcap: float
+    layers: tuple                      # of dicts, validated
+    loop: Optional[tuple] = None       # (start, stop, times)
+    max_position: int = 131072
+    eos_token_id: Optional[int] = None
+
+    MIXERS = ("attention", "gla")
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "FopivikConfig":
+        norm = _take(d, "norm", dict)
+        layers = _take(d, "layers", list)
+        if not layers:
+            raise ConfigError("config.json: 'layers' must list at least one layer")
+        out = []
+        for i, layer in enumerate(layers):
+            where = f"layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"config.json: {where} must be an object")
+            kind = _take(layer, "type", str)
+            m = _take(layer, "mixer", dict)
+            if kind == "attention":
+                mixer = {k: _take(m, k, int) for k in ("heads", "kv_heads", "dim", "vdim")}
+                mixer["scale"] = _take(m, "scale", float)
+                mixer["softcap"] = _take(m, "softcap", float)
+                mask, rot = _take(m, "mask", dict), _take(m, "rot", dict)
+                mixer["window"], mixer["keep_first"] = _take(mask, "size", int), _take(mask, "keep_first", int, 0)
+                mixer["rot_dims"], mixer["rot_base"] = _take(rot, "dims", int), _take(rot, "base", float)
+                sc = rot.get("scaling")
+                mixer["rot_scaling"] = None if sc is None else {k: _take(sc, k, float) for k in ("factor", "low", "high", "original")}
+                if min(mixer[k] for k in ("heads", "kv_heads", "dim", "vdim", "window")) <= 0 or mixer["heads"] % mixer["kv_heads"]:
+                    raise ConfigError(f"config.json: {where}.mixer: sizes must be positive and heads a multiple of kv_heads")
+                if mixer["keep_first"] < 0 or mixer["softcap"] <= 0:
+                    raise ConfigError(f"config.json: {where}.mixer: keep_first must not be negative and softcap must be positive")
+                if mixer["rot_dims"] < 0 or mixer["rot_dims"] % 2 or mixer["rot_dims"] > mixer["dim"]:
+                    raise ConfigError(f"config.json: {where}.mixer.rot.dims must be even and at most dim")
+            elif kind == "gla":
+                mixer = {k: _take(m, k, int) for k in ("heads", "dim", "vdim")}
+                mixer["tau"] = _take(m, "tau", float)
+                if min(mixer[k] for k in ("heads", "dim", "vdim")) <= 0 or not mixer["tau"] > 0:
+                    raise ConfigError(f"config.json: {where}.mixer: sizes and tau must be positive")
+            else:
+                raise ConfigError(f"config.json: {where}.type '{kind}' is not a mixer of this design {cls.MIXERS}")
+            ff = layer.get("mlp")
+            out.append({"type": kind, "mixer": mixer, "mlp": None if ff is None else _moe_of(ff, where)})
+        loop = d.get("loop")
+        if loop is not None:
+            if not isinstance(loop, dict):
+                raise ConfigError("config.json: 'loop' must be an object or null")
+            loop = (_take(loop, "start", int), _take(loop, "stop", int), _take(loop, "times", int))
+            if not (0 <= loop[0] < loop[1] <= len(out)) or loop[2] < 1:
+                raise ConfigError(f"config.json: loop {loop} does not name layers of this model, or runs them less than once")
+        eos = d.get("eos_token_id")
+        cfg = cls(architecture=_take(d, "architecture", str), width=_take(d, "width", int), vocab=_take(d, "vocab", int),
+                  norm_eps=_take(norm, "eps", float), residual_mult=_take(d, "residual_mult", float),
+                  logit_softcap=_take(d, "logit_softcap", float), layers=tuple(out), loop=loop,
+                  max_position=_take(d, "max_position", int, 131072), eos_token_id=eos if isinstance(eos, int) else None)
+        if cfg.width <= 0 or cfg.vocab <= 0 or cfg.max_position <= 0 or cfg.logit_softcap <= 0:
+            raise ConfigError("config.json: width, vocab, max_position and logit_softcap must be positive")
+        return cfg
+
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_position
+
+
 @dataclass(frozen=True)
 class Architecture:
     """One registry entry: how to read the config and how to lay the model out."""

@@ -9,7 +9,10 @@
 // (kernel/attention/attention_NH_32_NKV_4_HS_64.h:169-172,228-232); scores are scaled
 // by the given factor instead of the reference's constant for head size 64 (:197).
 // This is the attention of the 32-bit path and of bfloat16 shapes that the tensor-core
-// kernels refuse.
+// kernels refuse.  Options, all off at zero: values of another size than the keys (vdim); a soft cap
+// on the scaled scores, s <- cap * tanh(s / cap); a sink, a key with score 0 and no value that only
+// adds 1 to the softmax's denominator; and, with a window, the first keep_first keys of the request,
+// which stay visible (at their true positions) after the window has passed them.
 #include "common.cuh"
 
 namespace {
@@ -66,7 +69,8 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                int table_width, const int* __restrict__ token_entry,
                                const int* __restrict__ positions, int n_tokens, int n_heads, int n_kv,
-                               int head_dim, int page_size, int window, float scale, bool vec) {
+                               int head_dim, int vdim, int page_size, int window, int keep_first, float scale,
+                               float softcap, int sink, bool vec) {
   __shared__ float q_s[WARPS][MAXD];
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
@@ -78,6 +82,9 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
   const int pos = positions[t];
   const int* table = block_table + (size_t)token_entry[t] * table_width;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int keep_end = min(keep_first, lo);      // keys [0, keep_end) lie before the window and are seen all the same
+  const int lo_tile = (lo / 32) * 32;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
 
   const T* q_row = q + (size_t)t * q_stride + (size_t)h * head_dim;
   for (int d = lane; d < head_dim; d += 32) q_s[warp][d] = to_f32(q_row[d]);
@@ -86,17 +93,24 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
   float acc[MAXD / 32];
 #pragma unroll
   for (int i = 0; i < MAXD / 32; ++i) acc[i] = 0.f;
-  float m = -INFINITY, l = 0.f;
+  // the sink is the first term of the softmax: score 0, weight exp(0 - m), no value
+  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
 
-  for (int tile = (lo / 32) * 32; tile <= pos; tile += 32) {
+  for (int tile = keep_end > 0 ? 0 : lo_tile; tile <= pos; tile += 32) {
+    if (tile >= keep_end && tile < lo_tile) {      // between the kept keys and the window: nothing to see
+      tile = lo_tile - 32;
+      continue;
+    }
     const int kp = tile + lane;
-    const bool valid = kp >= lo && kp <= pos;
-    long long row = 0;
+    const bool valid = kp <= pos && (kp >= lo || kp < keep_end);
+    long long row = 0;                             // the key's place in units of rows: times head_dim or vdim
     float s = -INFINITY;
     if (valid) {
       const int page = table[kp / page_size];
-      row = (((long long)page * n_kv + g) * page_size + kp % page_size) * head_dim;
-      s = (vec ? dot_row<T>(q_s[warp], k_pages + row, head_dim) : dot_row_scalar<T>(q_s[warp], k_pages + row, head_dim)) * scale;
+      row = ((long long)page * n_kv + g) * page_size + kp % page_size;
+      const T* k_row = k_pages + row * head_dim;
+      s = (vec ? dot_row<T>(q_s[warp], k_row, head_dim) : dot_row_scalar<T>(q_s[warp], k_row, head_dim)) * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float alpha = expf(m - m_new);  // m = -inf at the first tile gives 0
@@ -110,57 +124,65 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const long long rj = __shfl_sync(0xffffffffu, row, j);
       if (pj != 0.f) {
-        const T* v = v_pages + rj;
+        const T* v = v_pages + rj * vdim;
 #pragma unroll
         for (int i = 0; i < MAXD / 32; ++i) {
           const int d = lane + 32 * i;
-          if (d < head_dim) acc[i] = fmaf(pj, to_f32(v[d]), acc[i]);
+          if (d < vdim) acc[i] = fmaf(pj, to_f32(v[d]), acc[i]);
         }
       }
     }
   }
   const float inv = 1.f / l;
-  T* o = out + (size_t)t * out_stride + (size_t)h * head_dim;
+  T* o = out + (size_t)t * out_stride + (size_t)h * vdim;
 #pragma unroll
   for (int i = 0; i < MAXD / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < head_dim) o[d] = from_f32<T>(acc[i] * inv);
+    if (d < vdim) o[d] = from_f32<T>(acc[i] * inv);
   }
 }
 
 }  // namespace
 
-// q [n_tokens, q_stride] with head h at column h*head_dim; out [n_tokens, out_stride] likewise.
-// k_pages / v_pages [pages, n_kv, page_size, head_dim]; block_table [entries, table_width] holds,
+// q [n_tokens, q_stride] with head h at column h*head_dim; out [n_tokens, out_stride] with head h at column
+// h*vdim.  k_pages [pages, n_kv, page_size, head_dim], v_pages [pages, n_kv, page_size, vdim]; block_table [entries, table_width] holds,
 // for batch entry e, the page of positions [i*page_size, (i+1)*page_size) at column i.
 LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const void* q, long long q_stride,
                                           const void* k_pages, const void* v_pages, const int* block_table,
                                           int table_width, const int* token_entry, const int* positions,
-                                          int n_tokens, int n_heads, int n_kv, int head_dim, int page_size,
-                                          int window, float scale, int dtype, cudaStream_t stream) {
+                                          int n_tokens, int n_heads, int n_kv, int head_dim, int vdim, int page_size,
+                                          int window, int keep_first, float scale, float softcap, int sink, int dtype,
+                                          cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   LLMK_REQUIRE(head_dim > 0 && head_dim <= MAX_HEAD_DIM, "paged_attention: head_dim %d must be 1 to %d", head_dim, MAX_HEAD_DIM);
   LLMK_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "paged_attention: %d query heads do not divide into %d kv heads",
                n_heads, n_kv);
+  LLMK_REQUIRE(vdim > 0 && vdim <= MAX_HEAD_DIM, "paged_attention: value size %d must be 1 to %d", vdim, MAX_HEAD_DIM);
   LLMK_REQUIRE(page_size > 0 && window >= 0, "paged_attention: bad page_size %d or window %d", page_size, window);
+  LLMK_REQUIRE(keep_first >= 0 && softcap >= 0.f, "paged_attention: bad keep_first %d or soft cap %f", keep_first, (double)softcap);
+  if (window == 0) keep_first = 0;
+  const int widest = head_dim > vdim ? head_dim : vdim;
   const long long items = (long long)n_tokens * n_heads;
   const long long blocks = (items + WARPS - 1) / WARPS;
   LLMK_REQUIRE(blocks < (1ll << 31), "paged_attention: too many (token, head) items");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     const bool vec = head_dim % (16 / (int)sizeof(T)) == 0 && (uintptr_t)k_pages % 16 == 0;      // whole 16-byte pieces per key row
-    if (head_dim <= 256)
+    if (widest <= 256)
       launch_kernel(paged_attention_generic_kernel<T, 256>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
-          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
-    else if (head_dim <= 512)      // the wide head of a latent attention (its rank)
+          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
+          softcap, sink, vec);
+    else if (widest <= 512)      // the wide head of a latent attention (its rank)
       launch_kernel(paged_attention_generic_kernel<T, 512>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
-          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
+          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
+          softcap, sink, vec);
     else
       launch_kernel(paged_attention_generic_kernel<T, MAX_HEAD_DIM>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
-          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale, vec);
+          table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
+          softcap, sink, vec);
     LLMK_LAUNCH_CHECK("paged_attention_generic");
   });
 }

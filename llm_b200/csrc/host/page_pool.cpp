@@ -15,15 +15,16 @@
 
 using namespace llmh;
 
+// keeps: per group the number of first tokens of a request that a window group never gives back (null: none).
 LLMH_API void* llmh_pool_create(int n_groups, const int* kinds, const int* page_sizes, const int* num_pages,
-                                const int* windows, int max_requests, int max_seq_len) {
+                                const int* windows, const int* keeps, int max_requests, int max_seq_len) {
   if (n_groups < 0 || max_requests <= 0 || max_seq_len <= 0) return nullptr;
   Pool* p = new Pool();
   p->max_requests = max_requests;
   p->max_seq_len = max_seq_len;
   for (int g = 0; g < n_groups; ++g) {
     if (page_sizes[g] <= 0 || num_pages[g] < 0 || (kinds[g] != KIND_FULL && kinds[g] != KIND_WINDOW) ||
-        (kinds[g] == KIND_WINDOW && windows[g] <= 0)) {
+        (kinds[g] == KIND_WINDOW && windows[g] <= 0) || (keeps && keeps[g] < 0)) {
       delete p;
       return nullptr;
     }
@@ -32,6 +33,7 @@ LLMH_API void* llmh_pool_create(int n_groups, const int* kinds, const int* page_
     grp.page_size = page_sizes[g];
     grp.num_pages = num_pages[g];
     grp.window = windows[g];
+    grp.keep = keeps ? keeps[g] : 0;
     grp.width = grp.pages_for(max_seq_len);
     grp.free.resize(num_pages[g]);
     for (int i = 0; i < num_pages[g]; ++i) grp.free[i] = num_pages[g] - 1 - i;      // page 0 is handed out first
@@ -217,7 +219,11 @@ LLMH_API int llmh_pool_check(void* h) {
       if (grp.n_pages[slot] != grp.pages_for(p->len[slot]))
         return p->fail(ERR_CONTRACT, "group %d: table of slot %d does not match its length", (int)g, slot);
       const int* row = grp.table.data() + (size_t)slot * grp.width;
-      for (int i = grp.first_live[slot]; i < grp.n_pages[slot]; ++i) {
+      for (int i = 0; i < grp.n_pages[slot]; ++i) {
+        if (i >= grp.keep_pages() && i < grp.first_live[slot]) {
+          if (row[i] != -1) return p->fail(ERR_CONTRACT, "group %d: a page that was given back is still in the table", (int)g);
+          continue;
+        }
         if (row[i] < 0 || row[i] >= grp.num_pages)
           return p->fail(ERR_CONTRACT, "group %d: a live table entry is marked as given back", (int)g);
         ++seen[row[i]];

@@ -21,9 +21,12 @@ enum : int { ERR_CONTRACT = -1, ERR_OUT_OF_PAGES = -2 };
 
 struct Group {
   int kind, page_size, num_pages, window, width;     // width: table entries per request
+  int keep = 0;                                      // window groups: the request's first `keep` tokens are never given back
   std::vector<int> free;                             // LIFO: back() is handed out next
   std::vector<int> table;                            // [max_requests][width], -1 = given back / not held
-  std::vector<int> n_pages, first_live;              // per slot: logical pages in the table, first one still held
+  std::vector<int> n_pages, first_live;              // per slot: logical pages in the table, first one the window still holds
+  // A slot holds the logical pages i < n_pages with i < keep_pages() (they carry kept tokens) or i >= first_live.
+  int keep_pages() const { return kind == KIND_WINDOW ? (keep + page_size - 1) / page_size : 0; }
 
   int pages_for(int length) const { return (length + page_size - 1) / page_size; }
   // logical pages below this index can no longer be seen by a token at next_pos or later
@@ -69,7 +72,7 @@ struct Pool {
       if (grp.kind == KIND_WINDOW) {
         const int first = slot >= 0 ? grp.first_live[slot] : 0;
         const int dead = std::min(grp.dead_before(cur), have_hi);
-        give_back = std::max(0, dead - first);
+        give_back = std::max(0, dead - std::max(first, grp.keep_pages()));
       }
       out[g] = need_hi - have_hi - give_back;
     }
@@ -104,7 +107,7 @@ struct Pool {
       if (grp.kind != KIND_WINDOW) continue;
       int* row = grp.table.data() + (size_t)slot * grp.width;
       const int dead = std::min(grp.dead_before(cur), grp.n_pages[slot]);
-      for (int i = grp.first_live[slot]; i < dead; ++i) {
+      for (int i = std::max(grp.first_live[slot], grp.keep_pages()); i < dead; ++i) {
         give(g, row[i]);
         row[i] = -1;
       }
@@ -118,7 +121,8 @@ struct Pool {
     for (size_t g = 0; g < groups.size(); ++g) {
       Group& grp = groups[g];
       int* row = grp.table.data() + (size_t)slot * grp.width;
-      for (int i = grp.first_live[slot]; i < grp.n_pages[slot]; ++i) give(g, row[i]);
+      for (int i = 0; i < grp.n_pages[slot]; ++i)
+        if (i < grp.keep_pages() || i >= grp.first_live[slot]) give(g, row[i]);
       std::fill(row, row + grp.n_pages[slot], -1);
       grp.n_pages[slot] = 0;
       grp.first_live[slot] = 0;

@@ -158,6 +158,110 @@ def add_dyt(resid: torch.Tensor, delta, w: torch.Tensor, b: torch.Tensor, alpha:
                                c_int(rows), c_int(hidden), c_int(_kind(ref.dtype)), _stream()))
 
 
+def add_layernorm(resid: torch.Tensor, delta, post, mult: float, pre, out, rows: int, eps: float) -> None:
+    """LayerNorm (a weight, no bias, float32 statistics) on both sides of the residual sum:
+    resid[:rows] += mult * ln(delta; post) where delta (a tensor or a PartialSum) is given (post None: mult * delta);
+    out[:rows] = ln(resid; pre) where out is given."""
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    hidden = resid.shape[-1]
+    ref = out if out is not None else delta
+    if ref is None:
+        return
+    for w in (post, pre):
+        assert w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == hidden)
+    if isinstance(delta, PartialSum):
+        assert delta.cols == hidden and delta.rows == rows
+    elif delta is not None:
+        assert delta.is_contiguous() and delta.shape[-1] == hidden
+    if out is not None:
+        assert pre is not None and out.is_contiguous() and out.shape[-1] == hidden
+        assert delta is None or delta.dtype == out.dtype
+    d, parts, splits, stride = _split_args(delta)
+    _check(load().llmk_add_layernorm(_ptr(resid), d, parts, splits, stride, _ptr(post), c_float(mult), _ptr(pre), _ptr(out),
+                                     c_int(rows), c_int(hidden), c_float(eps), c_int(_kind(ref.dtype)), _stream()))
+
+
+def softcap(x: torch.Tensor, rows: int, cap: float) -> None:
+    """x[:rows] = cap * tanh(x / cap), float32 in place."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(load().llmk_softcap(_ptr(x), c_longlong(rows * x.shape[-1]), c_float(cap), _stream()))
+
+
+def concat_embedding(out: torch.Tensor, resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int) -> None:
+    """out[t] = [resid[t] rounded to out's dtype ; table[ids[t]]], width 2 * hidden."""
+    vocab, hidden = table.shape
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape[-1] == hidden and ids.dtype == torch.int32
+    assert out.is_contiguous() and out.shape[-1] == 2 * hidden and out.dtype == table.dtype and table.is_contiguous()
+    _check(load().llmk_concat_embedding(_ptr(out), _ptr(resid), _ptr(table), _ptr(ids), c_int(n_tokens), c_int(hidden),
+                                        c_int(vocab), c_int(_kind(out.dtype)), _stream()))
+
+
+def head_rmsnorm_gate(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, gate, rows: int, heads: int, eps: float) -> None:
+    """out[t, h] = x[t, h] / sqrt(mean(x[t, h]^2) + eps) * w * silu(gate[t, h]) per head of x float32 [rows, heads * n];
+    w float32 [n] is shared by the heads; gate (the dtype of out, rows may be strided) or None."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[-1] == x.shape[-1]
+    n = x.shape[-1] // heads
+    assert n * heads == x.shape[-1] and w.dtype == torch.float32 and w.numel() == n
+    if gate is not None:
+        _rows_contig(gate, "gate")
+        assert gate.dtype == out.dtype and gate.shape[1] == x.shape[-1]
+    _check(load().llmk_head_rmsnorm_gate(_ptr(out), _ptr(x), _ptr(w), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0),
+                                         c_int(rows), c_int(heads), c_int(n), c_float(eps), c_int(_kind(out.dtype)), _stream()))
+
+
+def rope_pairs_kv_write(qkv, freqs, positions: torch.Tensor, slot_map, k_pages, v_pages, n_tokens: int, n_heads: int,
+                        n_kv: int, dim: int, vdim: int, q_out=None) -> torch.Tensor:
+    """Rotate the neighbouring pairs (2i, 2i+1), i < len(freqs), of every q and k head by position * freqs[i] and store
+    k and v at slot_map in the pages (n_kv 0: queries only).  qkv is a tensor [T, >= n_heads*dim + n_kv*(dim+vdim)]
+    (q is then rotated in place unless q_out is given) or a PartialSum (q_out required).  Returns the rotated q."""
+    assert positions.dtype == torch.int32
+    width = n_heads * dim + n_kv * (dim + vdim)
+    if isinstance(qkv, PartialSum):
+        assert q_out is not None and qkv.cols >= width
+        src_stride = qkv.cols
+    else:
+        _rows_contig(qkv, "qkv")
+        assert qkv.shape[1] >= width
+        src_stride = qkv.stride(0)
+        if q_out is None:
+            q_out = qkv
+    _rows_contig(q_out, "q_out")
+    assert q_out.dtype == qkv.dtype
+    page = 1
+    if n_kv:
+        assert slot_map.dtype == torch.int32 and k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
+        assert k_pages.shape[1] == n_kv and k_pages.shape[3] == dim and v_pages.shape[3] == vdim
+        page = k_pages.shape[2]
+    pairs = 0 if freqs is None else freqs.numel()
+    assert freqs is None or (freqs.dtype == torch.float32 and freqs.is_contiguous())
+    d, parts, splits, stride = _split_args(qkv)
+    _check(load().llmk_rope_pairs_kv_write(d, parts, splits, stride, c_longlong(src_stride), _ptr(q_out), c_longlong(q_out.stride(0)),
+                                           _ptr(freqs), c_int(pairs), _ptr(positions), _ptr(slot_map), _ptr(k_pages), _ptr(v_pages),
+                                           c_int(n_tokens), c_int(n_heads), c_int(n_kv), c_int(dim), c_int(vdim), c_int(page),
+                                           c_int(_kind(qkv.dtype)), _stream()))
+    return q_out
+
+
+def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias, tau: float,
+             q_scale: float, state: torch.Tensor, state_slots: torch.Tensor, cu_tokens: torch.Tensor, n_entries: int) -> None:
+    """The gated-linear-attention recurrence over every entry's tokens (see recurrent.cu): q, k [T, heads*dim] and
+    v [T, heads*vdim] are column ranges of one projection (equal row strides), z float32 [T, heads*dim] the decay's
+    pre-activation (+ z_bias), state float32 [slots, heads, dim, vdim] read and written at state_slots[entry],
+    out float32 [T, heads*vdim]."""
+    heads, dim, vdim = state.shape[1], state.shape[2], state.shape[3]
+    for t in (q, k, v, z, out):
+        _rows_contig(t, "gla operand")
+    assert q.stride(0) == k.stride(0) == v.stride(0) and q.dtype == k.dtype == v.dtype
+    assert q.shape[1] == k.shape[1] == z.shape[1] == heads * dim and v.shape[1] == out.shape[1] == heads * vdim
+    assert z.dtype == out.dtype == state.dtype == torch.float32 and state.is_contiguous()
+    assert state_slots.dtype == cu_tokens.dtype == torch.int32
+    assert z_bias is None or (z_bias.dtype == torch.float32 and z_bias.numel() == heads * dim)
+    _check(load().llmk_gla_scan(_ptr(out), c_longlong(out.stride(0)), _ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), _ptr(z),
+                                c_longlong(z.stride(0)), _ptr(z_bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(state_slots),
+                                _ptr(cu_tokens), c_int(n_entries), c_int(heads), c_int(dim), c_int(vdim), c_int(_kind(q.dtype)),
+                                _stream()))
+
+
 ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
 
 
@@ -231,8 +335,9 @@ def moe_max_tiles(n_pairs: int, experts: int, tile: int = 0) -> int:
 
 
 def moe_route(h: torch.Tensor, w: torch.Tensor, bias, logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-              n_tokens: int, top: int) -> None:
-    """Router: logits = h @ w.T with float32 accumulation (the tensor-core product in bfloat16 where it takes the
+              n_tokens: int, top: int, over_all: bool = False) -> None:
+    """Router (over_all: the weights are the chosen experts' shares of the softmax over all experts, not
+    renormalised): logits = h @ w.T with float32 accumulation (the tensor-core product in bfloat16 where it takes the
     shape, the CUDA-core product otherwise) into `logits` (float32 [>= n_tokens, experts]); plus bias, the `top`
     largest per token (ids, falling) and the softmax over those alone (weights)."""
     _rows_contig(h, "h")
@@ -248,7 +353,7 @@ def moe_route(h: torch.Tensor, w: torch.Tensor, bias, logits: torch.Tensor, ids:
         z = logits
     d, parts, splits, stride = _split_args(z)
     _check(load().llmk_moe_topk(d, parts, splits, stride, _ptr(bias), _ptr(ids), _ptr(weights), c_int(n_tokens),
-                                c_int(experts), c_int(top), _stream()))
+                                c_int(experts), c_int(top), c_int(int(over_all)), _stream()))
 
 
 def moe_group(ids: torch.Tensor, n_pairs: int, experts: int, meta: torch.Tensor, tile_expert: torch.Tensor,
@@ -396,8 +501,11 @@ def rope_kv_write(qkv, cos, sin, positions: torch.Tensor, slot_map: torch.Tensor
 def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, token_entry: torch.Tensor, positions: torch.Tensor,
                             n_tokens: int, n_heads: int, n_kv: int, head_dim: int, window: int,
-                            scale: float) -> None:
-    """out[t, h*HS:(h+1)*HS] = causal (windowed) attention of q[t, h] over its request's pages."""
+                            scale: float, value_dim: int = 0, softcap: float = 0.0, sink: bool = False,
+                            keep_first: int = 0) -> None:
+    """out[t, h*VS:(h+1)*VS] = causal (windowed) attention of q[t, h] over its request's pages.  value_dim: size of a
+    value row where it differs from the keys' (0 = the same); softcap > 0: scores pass cap * tanh(s / cap); sink: the
+    softmax's denominator gets one more term of score 0; keep_first: with a window, the request's first keys stay visible."""
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert token_entry.dtype == torch.int32 and positions.dtype == torch.int32
@@ -405,8 +513,8 @@ def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.T
     _check(load().llmk_paged_attention_generic(
         _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(token_entry), _ptr(positions), c_int(n_tokens),
-        c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(k_pages.shape[2]), c_int(window or 0),
-        c_float(scale), c_int(_kind(q.dtype)), _stream()))
+        c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(value_dim or head_dim), c_int(k_pages.shape[2]), c_int(window or 0),
+        c_int(keep_first or 0), c_float(scale), c_float(softcap or 0.0), c_int(int(bool(sink))), c_int(_kind(q.dtype)), _stream()))
 
 
 def feed_tokens(token_ids: torch.Tensor, sampled: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, n: int) -> None:
@@ -558,12 +666,19 @@ def attention_tc_take_error() -> int:
 
 
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
-                    window: int, scale: float) -> None:
+                    window: int, scale: float, value_dim: int = 0, softcap: float = 0.0, sink: bool = False,
+                    keep_first: int = 0) -> None:
     """Attention of the step's tokens over their requests' pages; q is the first
     n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: in bfloat16 the
     split-key decode kernel when every entry brings one token and the tcgen05 kernel otherwise,
     where it takes the sizes; the general kernel for float32 and for all other sizes (head sizes
-    off the 16-grid among them)."""
+    off the 16-grid among them).  value_dim, softcap, sink, keep_first: see paged_attention_generic, the kernel
+    that takes them in every combination."""
+    if (value_dim and value_dim != head_dim) or softcap or sink or keep_first:
+        paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
+                                ctx.n_tokens, n_heads, n_kv, head_dim, window, scale, value_dim=value_dim,
+                                softcap=softcap, sink=sink, keep_first=keep_first)
+        return
     if ctx.decode_only and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256:
         max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
         if window:

@@ -1,0 +1,139 @@
+// Gated linear attention as a recurrence over a matrix state.
+//
+// Per request and head the state S [dim, vdim] (float32, one slot per live request) follows
+//     S_t = diag(a_t) S_{t-1} + k_t v_t^T,        o_t = S_t^T (q_t * q_scale),
+// where the decay a_t [dim] in (0, 1) acts on the rows of S (the key channels):
+//     a_t = sigmoid(z_t + b)^(1 / tau) = exp(logsigmoid(z_t + b) / tau).
+// The same kernel serves prompts, portions of prompts and single decoded tokens: it reads the
+// state its request left, walks the entry's tokens in order and writes the state back, so a
+// token's output is the same arithmetic however the tokens were cut into steps or batched.
+// Everything that enters the recurrence is float32: decay, its logarithm, state, sums; q, k, v
+// are read in the element kind of the projections.
+//
+// Work split: a CTA owns one (entry, head, tile of VT value columns); thread (j, g) keeps the 16
+// state rows d = 16 g .. 16 g + 15 of column j in registers.  Tokens are staged in shared memory
+// CHUNK at a time (q, k, a once per CTA, broadcast to the threads of a row group); each thread
+// updates its rows and keeps a partial o per token, and the partial sums of the row groups are
+// added in the order of g after every chunk.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROWS = 16;      // state rows per thread
+constexpr int CHUNK = 8;      // tokens staged at a time
+constexpr int MAX_GROUPS = 16;
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <typename T, int VT>
+__global__ void __launch_bounds__(VT * MAX_GROUPS)
+gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restrict__ q, const T* __restrict__ k,
+                const T* __restrict__ v, long long qkv_stride, const float* __restrict__ z, long long z_stride,
+                const float* __restrict__ z_bias, float inv_tau, float q_scale, float* __restrict__ state,
+                const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, int heads, int dim, int vdim) {
+  extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int groups = blockDim.y, dpad = groups * ROWS;
+  float* q_s = smem;                          // [CHUNK][dpad]
+  float* k_s = q_s + CHUNK * dpad;
+  float* a_s = k_s + CHUNK * dpad;
+  float* v_s = a_s + CHUNK * dpad;            // [CHUNK][VT]
+  float* part = v_s + CHUNK * VT;             // [CHUNK][groups][VT]
+  const int j = threadIdx.x, g = threadIdx.y;
+  const int tid = g * VT + j, nthreads = VT * groups;
+  const int entry = blockIdx.z, head = blockIdx.y, col = blockIdx.x * VT + j;
+  const int t0 = cu_tokens[entry], t1 = cu_tokens[entry + 1];
+  float* S_g = state + (((size_t)state_slots[entry] * heads + head) * dim) * vdim;
+  const bool col_ok = col < vdim;
+
+  float S[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int d = g * ROWS + i;
+    S[i] = (col_ok && d < dim) ? S_g[(size_t)d * vdim + col] : 0.f;
+  }
+  for (int c0 = t0; c0 < t1; c0 += CHUNK) {
+    const int n = min(CHUNK, t1 - c0);
+    __syncthreads();                          // the previous chunk's partial sums have been read
+    for (int idx = tid; idx < n * dpad; idx += nthreads) {
+      const int c = idx / dpad, d = idx % dpad;
+      float qv = 0.f, kv = 0.f, av = 0.f;
+      if (d < dim) {
+        const size_t at = (size_t)(c0 + c) * qkv_stride + (size_t)head * dim + d;
+        qv = to_f32(q[at]) * q_scale;
+        kv = to_f32(k[at]);
+        const float zz = z[(size_t)(c0 + c) * z_stride + (size_t)head * dim + d] + (z_bias ? z_bias[head * dim + d] : 0.f);
+        av = expf(log_sigmoid(zz) * inv_tau);
+      }
+      q_s[idx] = qv; k_s[idx] = kv; a_s[idx] = av;
+    }
+    for (int idx = tid; idx < n * VT; idx += nthreads) {
+      const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
+      v_s[idx] = cc < vdim ? to_f32(v[(size_t)(c0 + c) * qkv_stride + (size_t)head * vdim + cc]) : 0.f;
+    }
+    __syncthreads();
+    for (int c = 0; c < n; ++c) {
+      const float vv = v_s[c * VT + j];
+      const float* qc = q_s + c * dpad + g * ROWS;
+      const float* kc = k_s + c * dpad + g * ROWS;
+      const float* ac = a_s + c * dpad + g * ROWS;
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) {
+        S[i] = fmaf(ac[i], S[i], kc[i] * vv);
+        o = fmaf(S[i], qc[i], o);
+      }
+      part[(c * groups + g) * VT + j] = o;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < n * VT; idx += nthreads) {
+      const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
+      if (cc >= vdim) continue;
+      float o = 0.f;
+      for (int gg = 0; gg < groups; ++gg) o += part[(c * groups + gg) * VT + jj];
+      out[(size_t)(c0 + c) * out_stride + (size_t)head * vdim + cc] = o;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int d = g * ROWS + i;
+    if (col_ok && d < dim) S_g[(size_t)d * vdim + col] = S[i];
+  }
+}
+
+}  // namespace
+
+// out float32 [tokens, out_stride] with head h at column h * vdim.  q, k (head h at column h * dim) and v (head h at
+// column h * vdim) are rows of the element kind, qkv_stride elements apart.  z float32 [tokens, z_stride], the
+// decay's pre-activation, head h at column h * dim; z_bias float32 [heads * dim] or null.  state float32
+// [slots, heads, dim, vdim]; state_slots [entries]; cu_tokens [entries + 1]: entry e owns tokens cu[e] .. cu[e+1]-1.
+// A launch that 32 columns a tile would leave with fewer CTAs than SMs takes narrower tiles (16, 8); the sums of
+// a column do not depend on the tile's width.
+LLMK_API int llmk_gla_scan(float* out, long long out_stride, const void* q, const void* k, const void* v,
+                           long long qkv_stride, const float* z, long long z_stride, const float* z_bias, float tau,
+                           float q_scale, float* state, const int* state_slots, const int* cu_tokens, int n_entries,
+                           int heads, int dim, int vdim, int dtype, cudaStream_t stream) {
+  if (n_entries == 0) return 0;
+  LLMK_REQUIRE(heads > 0 && dim > 0 && vdim > 0, "gla_scan: sizes must be positive");
+  LLMK_REQUIRE(dim <= ROWS * MAX_GROUPS, "gla_scan: key size %d exceeds %d", dim, ROWS * MAX_GROUPS);
+  LLMK_REQUIRE(tau > 0.f, "gla_scan: tau must be positive");
+  LLMK_REQUIRE(n_entries <= 65535 && heads <= 65535, "gla_scan: too many entries or heads for one launch");
+  const int groups = (dim + ROWS - 1) / ROWS;
+  const long long wide = (long long)((vdim + 31) / 32) * heads * n_entries;
+  const int sms = llmk_sm_count();
+  const int vt = wide >= sms ? 32 : (wide * 2 >= sms ? 16 : 8);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    auto launch = [&](auto kern, int VT) {
+      const size_t smem = sizeof(float) * ((size_t)CHUNK * groups * ROWS * 3 + (size_t)CHUNK * VT + (size_t)CHUNK * groups * VT);
+      return launch_kernel(kern, dim3((vdim + VT - 1) / VT, heads, n_entries), dim3(VT, groups), smem, stream, out, out_stride,
+                           (const T*)q, (const T*)k, (const T*)v, qkv_stride, z, z_stride, z_bias, 1.f / tau, q_scale, state,
+                           state_slots, cu_tokens, heads, dim, vdim);
+    };
+    if (vt == 32) launch(gla_scan_kernel<T, 32>, 32);
+    else if (vt == 16) launch(gla_scan_kernel<T, 16>, 16);
+    else launch(gla_scan_kernel<T, 8>, 8);
+    LLMK_LAUNCH_CHECK("gla_scan");
+  });
+}

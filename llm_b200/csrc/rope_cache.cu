@@ -118,3 +118,79 @@ LLMK_API int llmk_rope_kv_write(const void* qkv, const float* partials, int spli
     LLMK_LAUNCH_CHECK("rope_kv_write");
   });
 }
+
+// ---- rotation of neighbouring pairs, from frequencies -------------------------------------
+// The other common layout of RoPE: channels 2i and 2i+1 of a head form a pair (not i and i + HS/2),
+// only the first 2 * rot_pairs channels of a head turn, and the angle is position * freqs[i], one
+// float32 product, with freqs given by the caller (so any scaling of the frequencies is the caller's
+// business and no table bounds the position).  Keys and values may differ in size: a row of the
+// source holds n_heads * dim query channels, n_kv * dim key channels, n_kv * vdim value channels.
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_pairs_kv_write_kernel(MaybePartial<T> src, long long src_stride, T* __restrict__ q_out, long long q_out_stride,
+                           const float* __restrict__ freqs, int rot_pairs, const int* __restrict__ positions,
+                           const int* __restrict__ slot_map, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                           int n_heads, int n_kv, int dim, int vdim, int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float pos = (float)positions[t];
+  const size_t row = (size_t)t * src_stride;
+  T* q_row = q_out + (size_t)t * q_out_stride;
+  size_t k_base = 0, v_base = 0;
+  if (n_kv) {
+    const int slot = slot_map[t];
+    const size_t page = slot / page_size, off = slot % page_size;
+    k_base = (page * n_kv * page_size + off) * dim;           // + g * page_size * dim
+    v_base = (page * n_kv * page_size + off) * vdim;
+  }
+  const int pairs = (dim + 1) / 2;
+  for (int idx = threadIdx.x; idx < (n_heads + n_kv) * pairs; idx += blockDim.x) {
+    const int head = idx / pairs, i = idx % pairs;
+    const int d0 = 2 * i, d1 = d0 + 1;
+    const size_t h = row + (size_t)head * dim;
+    float a = src.at(h + d0), b = d1 < dim ? src.at(h + d1) : 0.f;
+    if (i < rot_pairs && d1 < dim) {
+      float s, c;
+      sincosf(pos * freqs[i], &s, &c);
+      const float ra = a * c - b * s, rb = b * c + a * s;
+      a = ra;
+      b = rb;
+    }
+    T* dst = head < n_heads ? q_row + (size_t)head * dim
+                            : k_pages + k_base + (size_t)(head - n_heads) * page_size * dim;
+    dst[d0] = from_f32<T>(a);
+    if (d1 < dim) dst[d1] = from_f32<T>(b);
+  }
+  const size_t v = row + (size_t)(n_heads + n_kv) * dim;
+  for (int idx = threadIdx.x; idx < n_kv * vdim; idx += blockDim.x) {
+    const int g = idx / vdim, d = idx % vdim;
+    v_pages[v_base + (size_t)g * page_size * vdim + d] = from_f32<T>(src.at(v + idx));
+  }
+}
+
+}  // namespace
+
+// qkv / partials as in llmk_rope_kv_write; q_out may be the source itself (a pair is read and written by
+// one thread).  freqs float32 [rot_pairs]; k_pages [pages, n_kv, page_size, dim], v_pages [.., vdim];
+// n_kv 0: only the queries are rotated and nothing is stored.
+LLMK_API int llmk_rope_pairs_kv_write(const void* qkv, const float* partials, int splits, long long split_stride,
+                                      long long src_stride, void* q_out, long long q_out_stride, const float* freqs,
+                                      int rot_pairs, const int* positions, const int* slot_map, void* k_pages,
+                                      void* v_pages, int n_tokens, int n_heads, int n_kv, int dim, int vdim,
+                                      int page_size, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  LLMK_REQUIRE((qkv != nullptr) != (partials != nullptr), "rope_pairs_kv_write: give qkv or partials");
+  LLMK_REQUIRE(rot_pairs >= 0 && 2 * rot_pairs <= dim, "rope_pairs_kv_write: %d pairs do not fit a head of %d", rot_pairs, dim);
+  LLMK_REQUIRE(rot_pairs == 0 || freqs != nullptr, "rope_pairs_kv_write: frequencies are missing");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> src{(const T*)qkv, partials, splits, split_stride};
+    launch_kernel(rope_pairs_kv_write_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, src, src_stride, (T*)q_out,
+                  q_out_stride, freqs, rot_pairs, positions, slot_map, (T*)k_pages, (T*)v_pages, n_heads, n_kv, dim,
+                  vdim, page_size);
+    LLMK_LAUNCH_CHECK("rope_pairs_kv_write");
+  });
+}

@@ -3,7 +3,8 @@
 //
 //   route    z = h Wr^T + b with float32 accumulation (the engine's product kernels make h Wr^T); the
 //            `top` largest z of a token (ties to the lower index); their weights are the softmax
-//            over those `top` values alone.
+//            over those `top` values alone, or (over_all) their shares of the softmax over every
+//            expert, which then do not sum to one.
 //   group    every (token, choice) pair gets a slot in a list that is sorted by expert, each
 //            expert's run padded to whole tiles of 64 slots, so that a tile of the products below
 //            belongs to one expert.  The launch sizes depend on the numbers of tokens, choices and
@@ -34,7 +35,7 @@ __device__ __forceinline__ float act_of(float z, int kind) {
 // product that made them) plus the bias, then `top` rounds of arg-max over the warp.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 topk_kernel(MaybePartial<float> z, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
-            int n_tokens, int experts, int top) {
+            int n_tokens, int experts, int top, int over_all) {
   __shared__ float z_s[ROUTE_WARPS][MAX_EXPERTS];
   pdl_launch_dependents();
   pdl_wait();
@@ -43,7 +44,15 @@ topk_kernel(MaybePartial<float> z, const float* __restrict__ bias, int* __restri
   if (t >= n_tokens) return;
   for (int e = lane; e < experts; e += 32) z_s[warp][e] = z.at((size_t)t * experts + e) + (bias ? bias[e] : 0.f);
   __syncwarp();
-  float z_max = 0.f, denom = 0.f;
+  float z_max = 0.f, denom = 0.f, denom_all = 0.f;
+  if (over_all) {                                     // the softmax's denominator over every expert, before any is struck out
+    float mx = -INFINITY;
+    for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z_s[warp][e]);
+    mx = warp_max(mx);
+    float s = 0.f;
+    for (int e = lane; e < experts; e += 32) s += expf(z_s[warp][e] - mx);
+    denom_all = warp_sum(s);
+  }
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
@@ -68,7 +77,7 @@ topk_kernel(MaybePartial<float> z, const float* __restrict__ bias, int* __restri
     __syncwarp();
   }
   if (lane == 0) {
-    const float inv = 1.f / denom;
+    const float inv = 1.f / (over_all ? denom_all : denom);
     for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] *= inv;
   }
 }
@@ -262,16 +271,16 @@ LLMK_API int llmk_moe_tile() { return TILE; }
 
 // logits float32 [n_tokens, experts], or the partial results [splits][n_tokens][experts] of the product that
 // makes them; bias float32 [experts] or null; ids int32 [n_tokens, top], weights float32 [n_tokens, top], both in
-// the order of falling logits.
+// the order of falling logits.  over_all: the weights are the chosen experts' shares of the softmax over all experts.
 LLMK_API int llmk_moe_topk(const float* logits, const float* partials, int splits, long long split_stride, const float* bias,
-                           int* ids, float* weights, int n_tokens, int experts, int top, cudaStream_t stream) {
+                           int* ids, float* weights, int n_tokens, int experts, int top, int over_all, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   LLMK_REQUIRE((logits != nullptr) != (partials != nullptr), "moe_topk: give logits or partials");
   LLMK_REQUIRE(experts > 0 && experts <= MAX_EXPERTS, "moe_topk: %d experts (1 to %d)", experts, MAX_EXPERTS);
   LLMK_REQUIRE(top > 0 && top <= experts, "moe_topk: top %d of %d experts", top, experts);
   MaybePartial<float> z{logits, partials, splits, split_stride};
   launch_kernel(topk_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream, z, bias, ids,
-                weights, n_tokens, experts, top);
+                weights, n_tokens, experts, top, over_all);
   LLMK_LAUNCH_CHECK("moe_topk");
 }
 

@@ -380,3 +380,170 @@ LLMK_API int llmk_act_rows(void* out, const void* in, const float* partials, int
     LLMK_LAUNCH_CHECK("act_rows");
   });
 }
+
+// ---- LayerNorm around a sublayer ------------------------------------------------
+// A block that norms a sublayer's output before it joins the residual, and norms the residual
+// before the next sublayer, needs per row
+//     resid += mult * ln(delta; post)        (post null: resid += mult * delta)
+//     out    = ln(resid; pre)                (out null: nothing more)
+// with ln(x; w) = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w: a weight, no bias, the
+// variance taken from the deviations (two passes over the row in shared memory).  Both halves are
+// optional, all arithmetic is float32, and a row is read from memory once.
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_layernorm_kernel(float* __restrict__ resid, MaybePartial<T> delta, const float* __restrict__ post, float mult,
+                     const float* __restrict__ pre, T* __restrict__ out, int hidden, float eps) {
+  extern __shared__ float row_s[];
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  const float inv_n = 1.f / (float)hidden;
+  if (delta.present()) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float v = delta.at(base + c);
+      row_s[c] = v;
+      s += v;
+    }
+    float mean = 0.f, rstd = 1.f;
+    if (post) {
+      mean = block_sum(s, scratch) * inv_n;
+      float q = 0.f;
+      for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float d = row_s[c] - mean;
+        q += d * d;
+      }
+      rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+    }
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float y = post ? (row_s[c] - mean) * rstd * post[c] : row_s[c];
+      const float r = fmaf(mult, y, resid[base + c]);
+      resid[base + c] = r;
+      row_s[c] = r;
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_s[c] = resid[base + c];
+  }
+  if (!out) return;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) s += row_s[c];
+  const float mean = block_sum(s, scratch) * inv_n;
+  float q = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float d = row_s[c] - mean;
+    q += d * d;
+  }
+  const float rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    out[base + c] = from_f32<T>((row_s[c] - mean) * rstd * pre[c]);
+}
+
+// delta: [rows, hidden] of the element kind, or float32 partial results, or neither; post, pre: float32
+// [hidden] or null; out: [rows, hidden] of the element kind or null (then pre is not read).
+LLMK_API int llmk_add_layernorm(float* resid, const void* delta, const float* partials, int splits, long long split_stride,
+                                const float* post, float mult, const float* pre, void* out, int rows, int hidden, float eps,
+                                int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  LLMK_REQUIRE(!(delta && partials), "add_layernorm: give delta or partials, not both");
+  LLMK_REQUIRE(out == nullptr || pre != nullptr, "add_layernorm: an output needs its weight");
+  const size_t smem = (size_t)hidden * sizeof(float);
+  LLMK_REQUIRE(smem <= 200 * 1024, "add_layernorm: rows of %d elements exceed the shared memory", hidden);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> d{(const T*)delta, partials, splits, split_stride};
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(add_layernorm_kernel<T>, dim3(rows), dim3(256), smem, stream, resid, d, post, mult, pre, (T*)out, hidden, eps);
+    LLMK_LAUNCH_CHECK("add_layernorm");
+  });
+}
+
+// ---- soft cap ---------------------------------------------------------------------
+// x = cap * tanh(x / cap), float32 in place: bounds logits to (-cap, cap) and leaves small ones alone.
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap, float inv_cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+LLMK_API int llmk_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  LLMK_REQUIRE(cap > 0.f, "softcap: the cap must be positive");
+  size_t blocks = ((size_t)n + 255) / 256;
+  if (blocks > (size_t)llmk_sm_count() * 16) blocks = (size_t)llmk_sm_count() * 16;
+  launch_kernel(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, (size_t)n, cap, 1.f / cap);
+  LLMK_LAUNCH_CHECK("softcap");
+}
+
+// ---- the stream beside the embedding ----------------------------------------------
+// out[t] = [ resid[t] rounded to the element kind ; table[ids[t]] ]: the input of a product that mixes
+// the stream with the embedding of the same token (width 2 * hidden).
+template <typename T>
+__global__ void concat_embedding_kernel(T* __restrict__ out, const float* __restrict__ resid, const T* __restrict__ table,
+                                        const int* __restrict__ ids, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;            // the embedding kernel has reported a bad id already
+  T* dst = out + (size_t)t * 2 * hidden;
+  const T* row = table + (size_t)(ok ? id : 0) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    dst[c] = from_f32<T>(resid[(size_t)t * hidden + c]);
+    dst[hidden + c] = ok ? row[c] : from_f32<T>(0.f);
+  }
+}
+
+LLMK_API int llmk_concat_embedding(void* out, const float* resid, const void* table, const int* ids, int n_tokens,
+                                   int hidden, int vocab, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(concat_embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)out, resid, (const T*)table, ids,
+                  hidden, vocab);
+    LLMK_LAUNCH_CHECK("concat_embedding");
+  });
+}
+
+// ---- RMS norm per head, gated -------------------------------------------------------
+// out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * w[:] * silu(gate[t, h, :]): the output stage
+// of a linear-attention mixer (x float32, one weight vector shared by the heads).  A warp per (t, h).
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_rmsnorm_gate_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                         const T* __restrict__ gate, long long gate_stride, long long items, int heads, int vdim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const long long t = item / heads;
+  const int h = (int)(item % heads);
+  const float* row = x + (size_t)item * vdim;
+  float ss = 0.f;
+  for (int c = lane; c < vdim; c += 32) ss += row[c] * row[c];
+  const float rstd = rsqrtf(warp_sum(ss) / (float)vdim + eps);
+  const T* g = gate ? gate + (size_t)t * gate_stride + (size_t)h * vdim : nullptr;
+  for (int c = lane; c < vdim; c += 32) {
+    float y = row[c] * rstd * w[c];
+    if (g) {
+      const float z = to_f32(g[c]);
+      y *= z / (1.f + expf(-z));
+    }
+    out[(size_t)item * vdim + c] = from_f32<T>(y);
+  }
+}
+
+LLMK_API int llmk_head_rmsnorm_gate(void* out, const float* x, const float* w, const void* gate, long long gate_stride,
+                                    int n_tokens, int heads, int vdim, float eps, int dtype, cudaStream_t stream) {
+  const long long items = (long long)n_tokens * heads;
+  if (items == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(head_rmsnorm_gate_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (T*)out, x, w,
+                  (const T*)gate, gate_stride, items, heads, vdim, eps);
+    LLMK_LAUNCH_CHECK("head_rmsnorm_gate");
+  });
+}

@@ -60,6 +60,7 @@ class GroupView:
     slot_map: torch.Tensor         # int32 [tokens]: page * page_size + offset of each new token
     kind: str = "full"
     window: Optional[int] = None
+    keep_first: int = 0            # window groups: the first tokens of a request whose pages stay
 
 
 @dataclass

@@ -163,9 +163,10 @@ class Engine:
         per_seq_full = (self.max_seq_len + self.page_size - 1) // self.page_size
         pages: List[int] = []
         cap = {}
-        for g, (kind, window) in enumerate(model.group_keys):
+        for g, (kind, window, keep) in enumerate(model.group_keys):
             if kind == "window":
-                per_seq = (window + self.max_tokens + self.page_size - 1) // self.page_size + 2
+                per_seq = (window + self.max_tokens + self.page_size - 1) // self.page_size + 2 + \
+                          (keep + self.page_size - 1) // self.page_size
                 cap[g] = self.max_entries * min(per_seq, per_seq_full)
             else:
                 cap[g] = self.max_entries * per_seq_full
@@ -174,20 +175,20 @@ class Engine:
         else:
             free, _total = torch.cuda.mem_get_info(self.device)
             budget = int(free * opt.gpu_memory_utilization) - self._activation_estimate()
-            for g, (kind, _w) in enumerate(model.group_keys):
+            for g, (kind, _w, _k) in enumerate(model.group_keys):
                 if kind == "window":
                     pages.append(cap[g])
                     budget -= cap[g] * bytes_per_page(model.cache_instances, g, self.page_size, self.dtype)
                 else:
                     pages.append(-1)
-            for g, (kind, _w) in enumerate(model.group_keys):
+            for g, (kind, _w, _k) in enumerate(model.group_keys):
                 if pages[g] < 0:
                     per = bytes_per_page(model.cache_instances, g, self.page_size, self.dtype)
                     pages[g] = max(0, min(cap[g], budget // max(per, 1)))
             if any(p <= 0 for p in pages):
                 raise RuntimeError("not enough free GPU memory for the cache pool")
-        specs = [GroupSpec(kind, self.page_size, pages[g], window)
-                 for g, (kind, window) in enumerate(model.group_keys)]
+        specs = [GroupSpec(kind, self.page_size, pages[g], window, keep)
+                 for g, (kind, window, keep) in enumerate(model.group_keys)]
         self.cache = CacheManager(specs, self.max_entries, self.max_seq_len)
         self.cache_storage = CacheStorage(model.cache_instances, pages, self.page_size, self.dtype, self.device)
         self.state_storage = StateStorage(model.state_needs, self.max_entries, self.device)
@@ -231,7 +232,8 @@ class Engine:
             g: GroupView(page_size=self.page_size,
                          block_table=dev(lay.block_table[g], lay.max_entries * w).view(lay.max_entries, w),
                          slot_map=dev(lay.slot_map[g], lay.max_tokens),
-                         kind=self.cache.group_spec(g).kind, window=self.cache.group_spec(g).window)
+                         kind=self.cache.group_spec(g).kind, window=self.cache.group_spec(g).window,
+                         keep_first=self.cache.group_spec(g).keep_first)
             for g, w in enumerate(lay.widths)
         }
         views = []

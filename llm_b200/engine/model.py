@@ -33,21 +33,21 @@ class Model:
         spec.validate()
         self.spec, self.dtype, self.device = spec, dtype, device
         self.embedding = build_part("embedding", spec.embedding, dtype, device)
-        self.blocks = [part_class("block", layer.block)(layer.parts, dtype, device) for layer in spec.layers]
+        self.blocks = [part_class("block", layer.block)(layer.parts, dtype, device, **layer.params) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, dtype, device) if spec.final_norm is not None else None
         self.head = build_part("head", spec.head, dtype, device)
 
         self._graph_askers = None
-        self.group_keys: List[tuple] = []            # (kind, window) per group
+        self.group_keys: List[tuple] = []            # (kind, window, keep_first) per group
         self.cache_instances: List[CacheInstance] = []
         self.state_needs: List[StateNeed] = []
         self.occurrences: List[Occurrence] = []
         latest: Dict[int, int] = {}                  # layer -> cache instance of its latest occurrence
         for layer_idx in spec.order:
             layer = spec.layers[layer_idx]
-            mixer = self.blocks[layer_idx].mixer
-            need: Optional[CacheNeed] = mixer.cache_need()
-            state: Optional[StateNeed] = mixer.state_need()
+            mixer = getattr(self.blocks[layer_idx], "mixer", None)      # a block without a mixer keeps nothing
+            need: Optional[CacheNeed] = mixer.cache_need() if mixer is not None else None
+            state: Optional[StateNeed] = mixer.state_need() if mixer is not None else None
             inst, owns = None, True
             if layer.cache_of is not None:
                 if need is not None:
@@ -62,7 +62,8 @@ class Model:
                 if key not in self.group_keys:
                     self.group_keys.append(key)
                 inst = len(self.cache_instances)
-                self.cache_instances.append(CacheInstance(self.group_keys.index(key), need.num_kv_heads, need.head_dim, need.values))
+                self.cache_instances.append(CacheInstance(self.group_keys.index(key), need.num_kv_heads, need.head_dim, need.values,
+                                                          need.value_dim or need.head_dim))
                 latest[layer_idx] = inst
             st = None
             if state is not None:

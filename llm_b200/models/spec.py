@@ -29,6 +29,7 @@ class LayerSpec:
     block: str
     parts: Dict[str, PartSpec]
     cache_of: Optional[int] = None
+    params: Dict[str, Any] = field(default_factory=dict)      # constants of the block arrangement itself
 
 
 @dataclass(frozen=True)

@@ -7,6 +7,13 @@ head attends to the keys of kv head h // (NH/NKV) that are at or before its own
 position and inside the window, if there is one
 (kernel/attention/attention_NH_32_NKV_4_HS_64.h:169-172,228-232); then the output
 projection (model/modules/Attention.h:19).  Sizes, window and scale are parameters.
+
+Further options, each a parameter and off by default: values of another size than the keys
+(value_dim); a soft cap on the scaled scores, s <- cap * tanh(s / cap); a sink, one more term of
+score 0 in the softmax's denominator that carries no value, so that a query may attend to
+nothing; first tokens of a request that stay visible after the window has passed them
+(keep_first; their pages are then never given back); a position part that turns neighbouring
+pairs of channels (kind "rope_pairs"); other tensor names.
 """
 from __future__ import annotations
 
@@ -19,12 +26,15 @@ from .base import CacheNeed, ParamInfo, Part, build_part, register_part
 from .linear import FUSE_PARTIALS, linear
 
 
+_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight"}
+
+
 class PagedAttention(Part):
     role = "mixer"
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position=None,
-                 window=None, scale=None, shares_cache: bool = False, bias: bool = False, prefix: str = "",
-                 dtype=None, device=None):
+                 window=None, scale=None, shares_cache: bool = False, bias: bool = False, value_dim=None, softcap=None,
+                 sink: bool = False, keep_first: int = 0, names=None, prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} heads do not divide into {num_kv_heads} kv heads")
@@ -35,8 +45,21 @@ class PagedAttention(Part):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.shares_cache = shares_cache          # reads another layer's pages: no k, v of its own
         self.position = build_part("position", position, dtype, device) if position is not None else None
+        self.value_dim = int(value_dim) if value_dim else head_dim
+        self.softcap = float(softcap) if softcap else 0.0
+        self.sink, self.keep_first = bool(sink), int(keep_first or 0)
+        if self.keep_first and not self.window:
+            self.keep_first = 0                   # without a window every token is seen anyway
+        self.names = dict(_NAMES, **(names or {}))
+        # the options above, and pair rotation, run on the path that rotates and stores with one kernel and
+        # attends with a kernel that takes them (see forward)
+        self.extended = bool(self.value_dim != head_dim or self.softcap or self.sink or self.keep_first
+                             or (self.position is not None and hasattr(self.position, "frequencies")))
+        if self.extended and (bias or (self.position is not None and not hasattr(self.position, "frequencies"))):
+            raise ValueError("attention: value_dim, softcap, sink and keep_first go with pair rotation or no positions, without biases")
         self.q_size = num_heads * head_dim
         self.kv_size = 0 if shares_cache else num_kv_heads * head_dim
+        self.v_size = 0 if shares_cache else num_kv_heads * self.value_dim
         self.bias = bool(bias)        # q/k/v and o projections carry bias vectors (model/modules/Attention.h:16-19)
         self.w_qkv = None
         self.w_o = None
@@ -44,11 +67,12 @@ class PagedAttention(Part):
         self.b_o = None
 
     def parameters(self):
-        p = {self.name("q_proj.weight"): ParamInfo((self.q_size, self.hidden_size))}
+        n = lambda k: self.name(self.names[k])
+        p = {n("q"): ParamInfo((self.q_size, self.hidden_size))}
         if not self.shares_cache:
-            p[self.name("k_proj.weight")] = ParamInfo((self.kv_size, self.hidden_size))
-            p[self.name("v_proj.weight")] = ParamInfo((self.kv_size, self.hidden_size))
-        p[self.name("o_proj.weight")] = ParamInfo((self.hidden_size, self.q_size))
+            p[n("k")] = ParamInfo((self.kv_size, self.hidden_size))
+            p[n("v")] = ParamInfo((self.v_size, self.hidden_size))
+        p[n("o")] = ParamInfo((self.hidden_size, self.num_heads * self.value_dim))
         if self.bias:
             p[self.name("q_proj.bias")] = ParamInfo((self.q_size,), kind="gain", init="normal")
             if not self.shares_cache:
@@ -58,11 +82,12 @@ class PagedAttention(Part):
         return p
 
     def bind(self, tensors):
-        parts = [tensors[self.name("q_proj.weight")]]
+        n = lambda k: tensors[self.name(self.names[k])]
+        parts = [n("q")]
         if not self.shares_cache:
-            parts += [tensors[self.name("k_proj.weight")], tensors[self.name("v_proj.weight")]]
+            parts += [n("k"), n("v")]
         self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0].contiguous()
-        self.w_o = tensors[self.name("o_proj.weight")].contiguous()
+        self.w_o = n("o").contiguous()
         if self.bias:
             names = ["q_proj.bias"] + ([] if self.shares_cache else ["k_proj.bias", "v_proj.bias"])
             self.b_qkv = torch.cat([tensors[self.name(n)] for n in names]).contiguous()
@@ -71,7 +96,8 @@ class PagedAttention(Part):
     def cache_need(self):
         if self.shares_cache:
             return None
-        return CacheNeed("window" if self.window else "full", self.num_kv_heads, self.head_dim, self.window)
+        return CacheNeed("window" if self.window else "full", self.num_kv_heads, self.head_dim, self.window,
+                         value_dim=self.value_dim, keep_first=self.keep_first)
 
     def state_need(self):
         return None
@@ -101,6 +127,8 @@ class PagedAttention(Part):
     def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
         T = ctx.n_tokens
         ws = ctx.workspace
+        if self.extended:
+            return self._forward_extended(x, ctx, view)
         width = self.q_size + 2 * self.kv_size
         cos = sin = None
         own_transform = None
@@ -139,6 +167,26 @@ class PagedAttention(Part):
                               q_rot=lambda: ws.get("q_rot", T, self.q_size, self.dtype))
         return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS,
                       bias=self.b_o)
+
+
+    def _forward_extended(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        """One product for q, k, v (its split-K partial results go unsummed to the next kernel); one kernel that
+        sums them, turns the pairs of q and k and stores k and v in the pages; the attention kernel that takes
+        the options; the output projection."""
+        T, ws = ctx.n_tokens, ctx.workspace
+        H, D, V = self.num_heads, self.head_dim, self.value_dim
+        k_pages, v_pages = view.k_pages, view.v_pages
+        n_kv = k_pages.shape[1]
+        qkv = linear(x, self.w_qkv, ws.get("qkv", T, self.q_size + self.kv_size + self.v_size, self.dtype), T,
+                     allow_partial=FUSE_PARTIALS)
+        freqs = self.position.frequencies() if self.position is not None else None
+        q = ops.rope_pairs_kv_write(qkv, freqs, ctx.positions, view.group.slot_map, k_pages, v_pages, T, H,
+                                    0 if self.shares_cache else n_kv, D, V,
+                                    q_out=ws.get("q_rot", T, self.q_size, self.dtype) if isinstance(qkv, ops.PartialSum) else None)
+        attn = ws.get("attn_out", T, H * V, self.dtype)
+        ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, H, n_kv, D, self.window or 0, self.scale,
+                            value_dim=V, softcap=self.softcap, sink=self.sink, keep_first=self.keep_first)
+        return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 
 register_part("mixer", "attention", PagedAttention)

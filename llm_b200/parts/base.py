@@ -17,7 +17,10 @@ Roles and what each must provide, beyond Part:
              ctx): its own in-place transform of the step's queries [T, heads, head_dim] and new
              keys [T, kv_heads, head_dim] (views of one buffer), run by the mixer between the
              projection and the cache store.  A part with neither leaves q and k as they are.
-  block      forward(stream, ctx, view): arranges norm / mixer / ffn on the stream.
+  block      forward(stream, ctx, view): arranges norm / mixer / ffn on the stream.  A block without a
+             mixer (attribute `mixer` None or absent) keeps no cache and no state.
+  stream     forward(stream, ctx): a transform of the whole residual stream between layers (the
+             re-entry of a looped stack, for one).
   embedding  forward(ctx, stream): fills the residual stream from token ids.
   head       logits(stream, ctx, final_norm, buffers) -> float32 logits [R, V] at ctx.logit_rows:
              everything after the last layer (row gather, final norm, projection, and whatever
@@ -47,6 +50,13 @@ class ParamInfo:
     shape: Tuple[int, ...]
     kind: str = "matrix"
     init: str = "normal"
+    free_dims: Tuple[int, ...] = ()     # dimensions whose size the checkpoint decides (config.json does not give it);
+                                        # shape holds there what random weights are drawn with
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(a == b or i in self.free_dims
+                                                     for i, (a, b) in enumerate(zip(shape, self.shape)))
 
 
 @dataclass(frozen=True)
@@ -59,9 +69,11 @@ class CacheNeed:
     head_dim: int
     window: Optional[int] = None
     values: bool = True       # False: one vector per token serves as key and as value (a latent), so no value pages exist
+    value_dim: Optional[int] = None     # size of a value row where it differs from a key row's
+    keep_first: int = 0       # with a window: the request's first tokens stay visible after the window has passed them
 
     def group_key(self):
-        return (self.kind, self.window)
+        return (self.kind, self.window, self.keep_first)
 
 
 @dataclass(frozen=True)
@@ -106,7 +118,7 @@ class Part:
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
-    role: {} for role in ("norm", "mixer", "ffn", "position", "block", "embedding", "head")
+    role: {} for role in ("norm", "mixer", "ffn", "position", "block", "embedding", "head", "stream")
 }
 
 
@@ -138,3 +150,17 @@ class ResidualStream:
         self.resid = resid            # [max_rows, H] float32
         self.rows = rows
         self.pending: Optional[torch.Tensor] = None   # [rows, H] compute dtype
+        # a pending term that is still to be normed and scaled before it joins the residual:
+        # (the norm part that does it, multiplier); None: the term is added as it is
+        self.pending_post = None
+
+    def fold(self, ctx) -> None:
+        """Add what is pending, so that resid is the whole stream."""
+        if self.pending is None:
+            return
+        if self.pending_post is not None:
+            self.pending_post[0].fold(self, ctx)
+        else:
+            from ..csrc import ops
+            ops.add_layernorm(self.resid, self.pending, None, 1.0, None, None, self.rows, 0.0)
+            self.pending = None

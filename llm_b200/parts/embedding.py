@@ -38,10 +38,11 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     role = "head"
 
-    def __init__(self, hidden_size: int, vocab_size: int, tied_to=None, weight_name: str = "weight", prefix: str = "",
-                 dtype=None, device=None):
+    def __init__(self, hidden_size: int, vocab_size: int, tied_to=None, weight_name: str = "weight", softcap=None,
+                 prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         self.hidden_size, self.vocab_size, self.tied_to = hidden_size, vocab_size, tied_to
+        self.softcap = float(softcap) if softcap else None      # logits <- cap * tanh(logits / cap)
         self.weight_name = weight_name        # "": the matrix is the tensor named like the part
         self.weight = None
 
@@ -63,13 +64,55 @@ class LMHead(Part):
         ctx.n_logit_rows rows, at addresses that stay fixed between steps."""
         rows, normed, out = buffers
         R = ctx.n_logit_rows
+        if stream.pending is not None and stream.pending_post is not None:
+            stream.fold(ctx)          # a term that is still to be normed cannot be gathered as it is
         ops.gather_rows(rows, stream.resid, stream.pending, ctx.logit_rows, R)
         if final_norm is not None:
             final_norm.forward_rows(rows, R, normed)
         else:
             ops.cast_rows(normed, rows, R)
-        return linear(normed, self.weight, out, R)
+        res = linear(normed, self.weight, out, R)
+        if self.softcap:
+            ops.softcap(out, R, self.softcap)
+        return res
 
 
+class EmbeddingReinjection(Part):
+    """x <- W [x ; e] + b_pass: the stream is mixed anew with the embedding e of the same tokens, as a stack of
+    layers that runs several times with the same weights does at the start of each pass.  W is
+    [hidden, 2 hidden] with the stream's half first; `steps` is [passes, hidden] and row `pass_index` of it
+    is added.  The product takes its inputs in the compute dtype and accumulates in float32; its result
+    replaces the float32 residual."""
+
+    role = "stream"
+
+    def __init__(self, hidden_size: int, vocab_size: int, passes: int, pass_index: int, table_name: str, in_name: str = "in",
+                 step_name: str = "step", prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if not (0 <= pass_index < passes):
+            raise ValueError(f"embedding re-injection: pass {pass_index} of {passes}")
+        self.hidden_size, self.vocab_size, self.passes, self.pass_index = hidden_size, vocab_size, passes, pass_index
+        self.table_name, self.in_name, self.step_name = table_name, in_name, step_name
+        self.table = self.w = self.step = None
+
+    def parameters(self):
+        return {self.table_name: ParamInfo((self.vocab_size, self.hidden_size)),
+                self.name(self.in_name): ParamInfo((self.hidden_size, 2 * self.hidden_size)),
+                self.name(self.step_name): ParamInfo((self.passes, self.hidden_size), kind="gain", init="normal")}
+
+    def bind(self, tensors):
+        self.table = tensors[self.table_name].contiguous()
+        self.w = tensors[self.name(self.in_name)].contiguous()
+        self.step = tensors[self.name(self.step_name)][self.pass_index].contiguous()
+
+    def forward(self, stream: ResidualStream, ctx) -> None:
+        T = stream.rows
+        stream.fold(ctx)
+        both = ctx.workspace.get("stream_and_embedding", T, 2 * self.hidden_size, self.dtype)
+        ops.concat_embedding(both, stream.resid, self.table, ctx.token_ids, T)
+        linear(both, self.w, stream.resid, T, bias=self.step)
+
+
+register_part("stream", "embedding_reinjection", EmbeddingReinjection)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("head", "lm_head", LMHead)

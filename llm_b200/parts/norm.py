@@ -82,3 +82,58 @@ class DynamicTanh(Part):
 
 
 register_part("norm", "dyt", DynamicTanh)
+
+
+class LayerNorm(Part):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w with a weight and no bias, the variance taken from the
+    deviations, everything in float32.  The part serves on both sides of a residual sum: `forward` norms
+    the stream for the next sublayer (adding first what is pending, like the other norms), and `attach`
+    leaves a sublayer's output pending on the stream as a term that is still to be normed by this part
+    and scaled by `mult` before it joins the residual: x += mult * ln(y).  The norm that comes next (or
+    `fold`) does both in one pass over the row.  The tensor is `<prefix>` unless a name is given."""
+
+    role = "norm"
+
+    def __init__(self, size: int, eps: float, weight_name: str = "", prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        self.size, self.eps = size, float(eps)
+        self.weight_name = weight_name
+        self.gain = None
+
+    def parameters(self):
+        return {self.name(self.weight_name): ParamInfo((self.size,), kind="gain", init="ones_normal")}
+
+    def bind(self, tensors):
+        self.gain = tensors[self.name(self.weight_name)].contiguous()
+
+    def _post(self, stream: ResidualStream):
+        """(post-norm weight, multiplier) of the stream's pending term."""
+        if stream.pending is None or stream.pending_post is None:
+            return None, 1.0
+        part, mult = stream.pending_post
+        if not isinstance(part, LayerNorm) or part.eps != self.eps:
+            raise ValueError("a pending term that another kind of norm is to treat cannot be folded by this one")
+        return part.gain, float(mult)
+
+    def forward(self, stream: ResidualStream, ctx, tag: str = "normed") -> torch.Tensor:
+        out = ctx.workspace.get(tag, stream.rows, self.size, self.dtype)
+        post, mult = self._post(stream)
+        ops.add_layernorm(stream.resid, stream.pending, post, mult, self.gain, out, stream.rows, self.eps)
+        stream.pending = stream.pending_post = None
+        return out
+
+    def attach(self, stream: ResidualStream, y, mult: float = 1.0) -> None:
+        stream.pending, stream.pending_post = y, (self, float(mult))
+
+    def fold(self, stream: ResidualStream, ctx) -> None:
+        """resid += mult * ln(pending): the stream made whole without a norm after it."""
+        post, mult = self._post(stream)
+        ops.add_layernorm(stream.resid, stream.pending, post, mult, None, None, stream.rows, self.eps)
+        stream.pending = stream.pending_post = None
+
+    def forward_rows(self, rows_f32: torch.Tensor, n_rows: int, out: torch.Tensor) -> torch.Tensor:
+        ops.add_layernorm(rows_f32, None, None, 1.0, self.gain, out, n_rows, self.eps)
+        return out
+
+
+register_part("norm", "layernorm", LayerNorm)

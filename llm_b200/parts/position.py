@@ -49,4 +49,52 @@ class RotaryEmbedding(Part):
 _TABLE_CACHE = {}
 
 
+class PairRotary(Part):
+    """RoPE on neighbouring pairs: channels 2i and 2i+1 of a head (i < dims/2) turn by position * f_i, the rest of
+    the head passes.  f_i = base^(-2i/dims), rescaled by wavelength l = 2 pi / f if `scaling` is given
+    ({factor, low, high, original}): kept where l < original/high, divided by factor where l > original/low,
+    and in between blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  The part
+    gives the frequencies (float32, evaluated in float64 and rounded once); the angle is one float32 product in
+    the kernel that rotates and stores, so no table bounds the position."""
+
+    role = "position"
+
+    def __init__(self, dims: int, base: float, scaling=None, prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if dims < 0 or dims % 2:
+            raise ValueError(f"pair rotation: dims {dims} must be even and not negative")
+        self.dims, self.base = int(dims), float(base)
+        self.scaling = dict(scaling) if scaling else None
+        if self.scaling:
+            for k in ("factor", "low", "high", "original"):
+                if k not in self.scaling:
+                    raise ValueError(f"pair rotation: scaling lacks '{k}'")
+            if self.scaling["high"] == self.scaling["low"]:
+                raise ValueError("pair rotation: scaling.high equals scaling.low")
+        self._freqs = None
+
+    def host_frequencies(self) -> np.ndarray:
+        i = np.arange(self.dims // 2, dtype=np.float64)
+        f = np.power(np.float64(self.base), -2.0 * i / max(self.dims, 1))
+        sc = self.scaling
+        if sc:
+            factor, low, high, orig = (float(sc[k]) for k in ("factor", "low", "high", "original"))
+            wave = 2.0 * np.pi / f
+            s = (orig / wave - low) / (high - low)
+            blended = (1.0 - s) * f / factor + s * f
+            f = np.where(wave < orig / high, f, np.where(wave > orig / low, f / factor, blended))
+        return f.astype(np.float32)
+
+    def frequencies(self):
+        """float32 [dims/2] on the device, or None when nothing turns."""
+        if self.dims == 0:
+            return None
+        if self._freqs is None:
+            self._freqs = torch.from_numpy(self.host_frequencies()).to(self.device).contiguous()
+        return self._freqs
+
+
+register_part("position", "rope_pairs", PairRotary)
+
+
 register_part("position", "rope", RotaryEmbedding)

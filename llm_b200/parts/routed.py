@@ -5,6 +5,9 @@
   w_e    = softmax over { z_e : e in S } (the chosen logits alone)
   out    = sum_{e in S} w_e * down_e(act(up_e(h)))  +  down_s(act_s(up_s(h)))   (shared, if any)
 
+Two further forms, both parameters: router "softmax_all", where w_e is expert e's share of the softmax over
+all experts (so the chosen weights do not sum to one), and gated experts, down_e(act(gate_e(h)) * up_e(h)).
+
 On the device: the router kernel writes each token's choices and weights; the (token, choice)
 pairs are sorted by expert into tiles of one expert each; the experts' up-projections run as
 one grouped product that gathers the tokens' rows and applies the activation; the
@@ -26,15 +29,20 @@ class RoutedFFN(Part):
     role = "ffn"
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, activation: str = "gelu",
-                 router_bias: bool = True, shared_size: int = 0, shared_activation: str = None, prefix: str = "",
-                 dtype=None, device=None):
+                 router_bias: bool = True, shared_size: int = 0, shared_activation: str = None, gated: bool = False,
+                 router: str = "softmax_chosen", prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         if not (0 < top <= experts <= 256):
             raise ValueError(f"routed feed-forward: top {top} of {experts} experts (1 <= top <= experts <= 256)")
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"routed feed-forward: unknown activation '{activation}'")
         self.hidden_size, self.experts, self.top, self.expert_size = hidden_size, experts, top, expert_size
+        if router not in ("softmax_chosen", "softmax_all"):
+            raise ValueError(f"routed feed-forward: unknown router '{router}'")
+        if gated and activation != "silu":
+            raise ValueError("routed feed-forward: gated experts take the silu activation")
         self.activation, self.router_bias = activation, bool(router_bias)
+        self.gated, self.over_all = bool(gated), router == "softmax_all"
         self.shared = (ActMLP(hidden_size, shared_size, shared_activation or activation, prefix=self.name("shared"),
                               dtype=dtype, device=device) if shared_size else None)
         self.w_router = self.b_router = self.w_up = self.w_down = None
@@ -47,6 +55,8 @@ class RoutedFFN(Part):
         if self.router_bias:
             p[self.name("router.b")] = ParamInfo((self.experts,), kind="gain", init="normal")
         for e in range(self.experts):
+            if self.gated:
+                p[self.name(f"e{e}.gate")] = ParamInfo((self.expert_size, self.hidden_size))
             p[self.name(f"e{e}.up")] = ParamInfo((self.expert_size, self.hidden_size))
             p[self.name(f"e{e}.down")] = ParamInfo((self.hidden_size, self.expert_size))
         return p
@@ -54,7 +64,11 @@ class RoutedFFN(Part):
     def bind(self, tensors):
         self.w_router = tensors[self.name("router")].contiguous()
         self.b_router = tensors[self.name("router.b")].contiguous() if self.router_bias else None
-        self.w_up = torch.stack([tensors[self.name(f"e{e}.up")] for e in range(self.experts)]).contiguous()
+        if self.gated:      # per expert [gate; up] stacked: one grouped product, then silu(gate) * up over the slots
+            self.w_up = torch.stack([torch.cat([tensors[self.name(f"e{e}.gate")], tensors[self.name(f"e{e}.up")]], dim=0)
+                                     for e in range(self.experts)]).contiguous()
+        else:
+            self.w_up = torch.stack([tensors[self.name(f"e{e}.up")] for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self.name(f"e{e}.down")] for e in range(self.experts)]).contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
@@ -74,15 +88,23 @@ class RoutedFFN(Part):
         y = ws.flat("moe_y", cap_slots * self.hidden_size, f32).view(cap_slots, self.hidden_size)
 
         logits = ws.get("moe_logits", T, E, f32)
-        ops.moe_route(x, self.w_router, self.b_router, logits, ids, wts, T, top)
+        ops.moe_route(x, self.w_router, self.b_router, logits, ids, wts, T, top, over_all=self.over_all)
         ops.moe_group(ids, pairs, E, meta, tile_expert, slot_src, pair_slot, max_tiles, tile)
+        # gated experts: the up product leaves [gate, up] per slot and a row kernel makes silu(gate) * up of it
+        up_out = (ws.flat("moe_gate_up", cap_slots * 2 * self.expert_size, self.dtype).view(cap_slots, 2 * self.expert_size)
+                  if self.gated else act)
+        up_act = None if self.gated else self.activation
         if tensor:
             rows = ws.flat("moe_rows", cap_slots * self.hidden_size, self.dtype).view(cap_slots, self.hidden_size)
             ops.moe_gather(rows, x, slot_src, meta, top, tile, max_tiles)
-            ops.moe_gemm_tc(rows, tile_expert, meta, self.w_up, act, max_tiles, act=self.activation)
+            ops.moe_gemm_tc(rows, tile_expert, meta, self.w_up, up_out, max_tiles, act=up_act)
+        else:
+            ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, up_out, max_tiles, act=up_act)
+        if self.gated:
+            ops.silu_mul(act[:max_tiles * tile], up_out[:max_tiles * tile], max_tiles * tile)
+        if tensor:
             ops.moe_gemm_tc(act, tile_expert, meta, self.w_down, y, max_tiles)
         else:
-            ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, act, max_tiles, act=self.activation)
             ops.moe_gemm(act, 0, slot_src, tile_expert, meta, self.w_down, y, max_tiles)
         shared = self.shared.forward(x, ctx, tag="ffn_shared") if self.shared is not None else None
         out = ws.get("ffn_out", T, self.hidden_size, self.dtype)

@@ -124,7 +124,7 @@ def load_tensors(model_dir: str, expected: Dict[str, ParamInfo], compute_dtype: 
         if name not in ck.where:
             continue
         e = ck.entry(name)
-        if tuple(e.shape) != tuple(info.shape):
+        if not info.fits(e.shape):
             wrong.append(f"{name}: file has {list(e.shape)}, model expects {list(info.shape)}")
         elif info.kind == "int_table" and e.dtype.is_floating_point:
             wrong.append(f"{name}: file has {e.dtype}, model expects an integer table")
@@ -149,7 +149,7 @@ def adopt_tensors(given: Dict[str, torch.Tensor], expected: Dict[str, ParamInfo]
     missing = sorted(n for n in expected if n not in given)
     unexpected = sorted(n for n in given if n not in expected)
     wrong = [f"{n}: given {list(given[n].shape)}, model expects {list(i.shape)}" for n, i in expected.items()
-             if n in given and tuple(given[n].shape) != tuple(i.shape)]
+             if n in given and not i.fits(given[n].shape)]
     if missing or unexpected or wrong:
         raise WeightError("the given tensors", missing, unexpected, wrong)
     return {n: given[n].to(device=device, dtype=_target_dtype(i, compute_dtype)).contiguous() for n, i in expected.items()}

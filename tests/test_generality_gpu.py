@@ -158,7 +158,7 @@ def test_toy_mixer_with_state_repeated_layers_and_shared_cache(tmp_path, dtype):
     model = eng.model
     assert len(model.state_needs) == 2                      # the toy layer runs twice: two states
     assert len(model.cache_instances) == 3                  # layer 0 twice, layer 2 once, none for the sharer
-    assert sorted(set(model.group_keys)) == [("full", None), ("window", 9)]
+    assert sorted(set(model.group_keys)) == [("full", None, 0), ("window", 9, 0)]
     for what, steps in (("whole", replay.steps_whole(reqs)), ("portions", replay.steps_portions(reqs)),
                         ("tail", replay.steps_tail_decode(reqs, tail=6)), ("mixed", replay.steps_mixed(reqs))):
         got = replay.run_steps(eng, steps)
