@@ -139,6 +139,14 @@ def route_all(h, w_r, top: int):
     return ids, vals
 
 
+def route_margin(h, w_r, top: int) -> torch.Tensor:
+    """Per token, how far the last chosen router logit lies above the first one left out (inf if none is left out)."""
+    z = torch.sort(h.to(F64) @ w_r.to(F64).T, dim=-1, descending=True).values
+    if top >= z.shape[-1]:
+        return torch.full((z.shape[0],), math.inf, dtype=F64)
+    return z[:, top - 1] - z[:, top]
+
+
 def gated_expert(h, w_gate, w_up, w_down):
     h = h.to(F64)
     return (torch.nn.functional.silu(h @ w_gate.to(F64).T) * (h @ w_up.to(F64).T)) @ w_down.to(F64).T
@@ -169,8 +177,9 @@ def layer_order(n_layers: int, loop: Optional[dict]):
     return out + [(i, None) for i in range(b, n_layers)]
 
 
-def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, return_layers: bool = False):
-    """Logits [T, vocab] of one whole sequence (and, if asked, the stream after every layer run)."""
+def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, return_layers: bool = False, margins=None):
+    """Logits [T, vocab] of one whole sequence (and, if asked, the stream after every layer run).  margins: a list
+    that receives, per routed feed-forward that runs, every token's routing margin."""
     eps, m = config["norm"]["eps"], config["residual_mult"]
     tok = torch.as_tensor(tokens, dtype=torch.long)
     T = tok.numel()
@@ -197,6 +206,8 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, return_layer
             n_e = ff["router"]["experts"]
             experts = [tuple(weights[f"{p}.mlp.e{j}.{n}"] for n in ("gate", "up", "down")) for j in range(n_e)]
             y = moe_ff(hn, weights[p + ".mlp.router"], ff["router"]["top"], experts)
+            if margins is not None:
+                margins.append(route_margin(hn, weights[p + ".mlp.router"], ff["router"]["top"]))
             x = x + m * layer_norm(y, weights[p + ".norm2b"], eps)
         streams.append(x.clone())
     z = layer_norm(x, weights["final.norm"], eps) @ weights["head"].to(F64).T

@@ -1,0 +1,580 @@
+"""GPU tests of the Fopivik design against the plain implementation (tests/plain_fopivik.py): each mechanism
+alone, then whole models under every way of cutting the work."""
+import math
+
+import pytest
+import torch
+
+import plain_fopivik as P
+import replay
+from fopivik_tiny import CONFIGS, config, layer, attn, gla, make_engine, make_weights, random_config
+from tiny import max_err, random_tokens
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 3e-5, "bfloat16": 5e-2}       # whole models, relative to the largest logit
+KTOL = {"float32": 4e-6, "bfloat16": 6e-3}      # kernels alone: one rounding of the output
+# In bfloat16 the router reads an input that differs from the float64 one by the rounding of everything before it, so a
+# token whose last chosen logit lies this close to the first one left out may be routed otherwise, and every later token
+# of the request, which reads that token through the attention or the state, inherits the difference.  Rows from the
+# first such token on prove nothing and are left out.  Float32 compares every row, and so does "bfloat16-all": the same
+# models with every expert chosen (the router's shares still weigh them), where no choice can flip.
+CLOSE_CALL = {"float32": 0.0, "bfloat16": 0.3, "bfloat16-all": 0.0}
+TOL["bfloat16-all"] = TOL["bfloat16"]
+DTYPES = ["float32", "bfloat16", "bfloat16-all"]
+
+
+def every_expert(cfg):
+    import copy
+    cfg = copy.deepcopy(cfg)
+    for lay in cfg["layers"]:
+        if lay["mlp"] is not None:
+            lay["mlp"]["router"]["top"] = lay["mlp"]["router"]["experts"]
+    return cfg
+
+
+def dev(t, dtype="float32"):
+    return t.to(device="cuda", dtype=DT[dtype]).contiguous()
+
+
+def bf(t):
+    return t.to(torch.bfloat16).float()
+
+
+def i32(xs):
+    return torch.tensor(xs, dtype=torch.int32, device="cuda")
+
+
+# ---- each mechanism alone ---------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,width", [(1, 8), (7, 100), (33, 256), (3, 2050)])
+def test_layernorm_on_both_sides_of_the_sum(dtype, rows, width):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(rows * 1000 + width)
+    x, y = torch.randn(rows, width, generator=g) * 3 + 0.5, bf(torch.randn(rows, width, generator=g) * 2 + 1.0)
+    post, pre = 1 + 0.2 * torch.randn(width, generator=g), 1 + 0.2 * torch.randn(width, generator=g)
+    eps, mult = 1e-5, 0.3
+    resid, out = dev(x), torch.empty(rows, width, device="cuda", dtype=DT[dtype])
+    ops.add_layernorm(resid, dev(y, dtype), dev(post), mult, dev(pre), out, rows, eps)
+    want = x.double() + mult * P.layer_norm(y, post, eps)
+    assert max_err(resid, want) < 2e-6
+    assert max_err(out, P.layer_norm(want, pre, eps)) < KTOL[dtype]
+    ops.add_layernorm(resid, None, None, 1.0, dev(pre), out, rows, eps)           # nothing pending: the stream stays
+    assert max_err(resid, want) < 2e-6 and max_err(out, P.layer_norm(want, pre, eps)) < KTOL[dtype]
+    ops.add_layernorm(resid, dev(y, dtype), dev(post), mult, None, None, rows, eps)      # fold alone
+    assert max_err(resid, want + mult * P.layer_norm(y, post, eps)) < 2e-6
+    resid = dev(x)
+    ops.add_layernorm(resid, dev(y, dtype), None, 1.0, None, None, rows, eps)     # a plain term
+    assert max_err(resid, x.double() + y.double()) < 1e-6
+
+
+def test_softcap_and_stream_beside_embedding():
+    from llm_b200.csrc import ops
+    z = torch.linspace(-90, 90, 7 * 33).view(7, 33)
+    x = dev(z)
+    ops.softcap(x, 7, 12.5)
+    assert max_err(x, 12.5 * torch.tanh(z.double() / 12.5)) < 1e-6
+    g = torch.Generator().manual_seed(3)
+    for dtype in ("float32", "bfloat16"):
+        table, resid = bf(torch.randn(19, 24, generator=g)), torch.randn(5, 24, generator=g)
+        ids = [3, 18, 0, 3, 7]
+        out = torch.empty(5, 48, device="cuda", dtype=DT[dtype])
+        ops.concat_embedding(out, dev(resid), dev(table, dtype), i32(ids), 5)
+        assert torch.equal(out[:, 24:].float().cpu(), table[ids])
+        assert max_err(out[:, :24], resid) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,n", [(1, 8), (3, 14), (2, 64), (5, 100)])
+def test_head_norm_with_gate(dtype, heads, n):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(heads * 100 + n)
+    rows = 9
+    x, w = torch.randn(rows, heads * n, generator=g) * 4, 1 + 0.2 * torch.randn(n, generator=g)
+    proj = bf(torch.randn(rows, heads * n + 24, generator=g))             # the gate is a column range of a wider product
+    gate = proj[:, 8:8 + heads * n]
+    out = torch.empty(rows, heads * n, device="cuda", dtype=DT[dtype])
+    ops.head_rmsnorm_gate(out, dev(x), dev(w), dev(proj, dtype)[:, 8:8 + heads * n], rows, heads, 1e-5)
+    want = (P.rms_unit(x.view(rows, heads, n), 1e-5) * w.double()).view(rows, -1) * torch.nn.functional.silu(gate.double())
+    assert max_err(out, want) < KTOL[dtype]
+
+
+SCALINGS = [None, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}, {"factor": 2.0, "low": 2.0, "high": 16.0, "original": 4096}]
+
+
+@pytest.mark.parametrize("scaling", SCALINGS)
+def test_scaled_frequencies_cover_all_three_ranges(scaling):
+    from llm_b200.parts.position import PairRotary
+    part = PairRotary(dims=48, base=50000.0, scaling=scaling, dtype=torch.float32, device=torch.device("cuda"))
+    want = P.scaled_frequencies(48, 50000.0, scaling)
+    assert max_err(part.frequencies(), want) < 1e-7
+    if scaling:
+        plain = P.scaled_frequencies(48, 50000.0, None)
+        ratio = want / plain
+        assert float(ratio.max()) == 1.0 and abs(float(ratio.min()) - 1 / scaling["factor"]) < 1e-12
+        assert int(((ratio < 1.0) & (ratio > 1 / scaling["factor"])).sum()) > 0        # some frequency is blended
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,D,V,rot", [(4, 2, 16, 8, 8), (3, 1, 10, 6, 10), (2, 2, 64, 64, 0), (5, 5, 7, 3, 6)])
+def test_pair_rotation_and_cache_store(dtype, H, G, D, V, rot):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(H * 100 + D)
+    T, page, n_pages = 11, 4, 9
+    width = H * D + G * (D + V)
+    qkv = bf(torch.randn(T, width + 5, generator=g))
+    positions = [0, 1, 2, 3, 4, 5, 700, 701, 702, 31, 32]
+    slots = torch.randperm(n_pages * page, generator=g)[:T].tolist()
+    freqs = P.scaled_frequencies(rot, 10000.0, SCALINGS[1]) if rot else None
+    k_pages = torch.zeros(n_pages, G, page, D, device="cuda", dtype=DT[dtype])
+    v_pages = torch.zeros(n_pages, G, page, V, device="cuda", dtype=DT[dtype])
+    x = dev(qkv, dtype)
+    q = ops.rope_pairs_kv_write(x, dev(freqs.float()) if rot else None, i32(positions), i32(slots), k_pages, v_pages, T, H, G, D, V)
+    pos = torch.tensor(positions)
+    q_in, k_in = qkv[:, :H * D].view(T, H, D), qkv[:, H * D:H * D + G * D].view(T, G, D)
+    v_in = qkv[:, H * D + G * D:width].view(T, G, V)
+    want_q = P.rotate_pairs(q_in, pos, freqs) if rot else q_in.double()
+    want_k = P.rotate_pairs(k_in, pos, freqs) if rot else k_in.double()
+    tol = 2e-5 if dtype == "float32" else 6e-3      # the angle is a float32 product: at position 700 its rounding shows
+    assert max_err(q[:, :H * D].view(T, H, D), want_q) < tol
+    for t, s in enumerate(slots):
+        assert max_err(k_pages[s // page, :, s % page], want_k[t]) < tol
+        assert torch.equal(v_pages[s // page, :, s % page].float().cpu(), v_in[t])
+
+
+def _paged(k, v, page, seed):
+    """k [T, G, D], v [T, G, V] of one request -> pages in a shuffled order and the block table row."""
+    T = k.shape[0]
+    n = -(-T // page)
+    order = torch.randperm(n + 3, generator=torch.Generator().manual_seed(seed))[:n].tolist()
+    k_pages = torch.full((n + 3, k.shape[1], page, k.shape[2]), 1e30)
+    v_pages = torch.full((n + 3, v.shape[1], page, v.shape[2]), 1e30)
+    for i, pg in enumerate(order):
+        m = min(page, T - i * page)
+        k_pages[pg, :, :m] = k[i * page:i * page + m].transpose(0, 1)
+        v_pages[pg, :, :m] = v[i * page:i * page + m].transpose(0, 1)
+    return k_pages, v_pages, order
+
+
+ATTN_CASES = [  # H, G, D, V, window, keep_first, softcap, sink, T
+    (4, 2, 16, 8, 12, 3, 20.0, True, 70),
+    (3, 1, 10, 6, 7, 0, 5.0, True, 40),
+    (2, 2, 64, 32, 33, 20, 0.0, True, 100),
+    (5, 5, 8, 24, 0, 0, 15.0, False, 50),
+    (2, 1, 32, 32, 1, 1, 30.0, True, 20),
+    (1, 1, 24, 40, 16, 40, 10.0, False, 90),
+    (8, 1, 64, 64, 40, 4, 20.0, True, 130),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_attention_with_sink_softcap_window_and_kept_tokens(dtype, case):
+    from llm_b200.csrc import ops
+    H, G, D, V, window, keep, cap, sink, T = case
+    g = torch.Generator().manual_seed(T * 7 + H)
+    page = 8
+    q, k, v = (bf(torch.randn(T, n, d, generator=g)) for n, d in ((H, D), (G, D), (G, V)))
+    scale = 2.0 / math.sqrt(D)
+    if window == 0 and not sink and not cap:
+        pytest.skip("nothing to test")
+    # the plain side: no window = a window longer than the request; no cap = a cap far above every score; no sink = its
+    # share taken out again
+    want = P.sink_attention(q, k, v, scale, cap or 1e9, window or T + 1, keep)
+    if not sink:
+        want_sink = want
+        s_sum = []
+        for i in range(T):
+            js = [j for j in range(i + 1) if P.visible(i, j, window or T + 1, keep)]
+            for h in range(H):
+                s = (k[js, h // (H // G)].double() @ q[i, h].double()) * scale
+                s = (cap or 1e9) * torch.tanh(s / (cap or 1e9))
+                s_sum.append(torch.exp(s).sum())
+        e = torch.stack(s_sum).view(T, H, 1)
+        want = want_sink * (1.0 + e) / e
+    k_pages, v_pages, order = _paged(k, v, page, T)
+    table = torch.full((2, len(order) + 2), -1, dtype=torch.int32)
+    table[1, :len(order)] = torch.tensor(order, dtype=torch.int32)
+    # queries in a shuffled order, as entry 1 of a batch: a row's result depends on its own position alone
+    rows = torch.randperm(T, generator=g).tolist()
+    out = torch.empty(T, H * V, device="cuda", dtype=DT[dtype])
+    ops.paged_attention_generic(out, dev(q.view(T, H * D)[rows], dtype), dev(k_pages, dtype), dev(v_pages, dtype), table.cuda(),
+                                i32([1] * T), i32(rows), T, H, G, D, window, scale, value_dim=V, softcap=cap, sink=sink,
+                                keep_first=keep)
+    assert max_err(out.view(T, H, V), want[rows]) < (1e-5 if dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,D,V,tau", [(2, 16, 24, 8.0), (1, 40, 8, 2.0), (3, 10, 14, 3.0), (2, 64, 128, 16.0), (1, 130, 33, 1.0)])
+def test_gla_recurrence_whole_cut_and_in_reused_slots(dtype, H, D, V, tau):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(H * 1000 + D)
+    lens = [37, 1, 18]
+    T = sum(lens)
+    proj = bf(torch.randn(T, 2 * H * D + H * V + 3, generator=g) * 0.7)
+    z, b = torch.randn(T, H * D, generator=g) * 2, torch.randn(H * D, generator=g)
+    q, k, v = proj[:, :H * D], proj[:, H * D:2 * H * D], proj[:, 2 * H * D:2 * H * D + H * V]
+    a = torch.exp(torch.nn.functional.logsigmoid(z.double() + b.double()) / tau)
+    want, at = [], 0
+    for n in lens:
+        sl = slice(at, at + n)
+        want.append(P.gla_recurrence(q[sl].view(n, H, D).double() * D ** -0.5, k[sl].view(n, H, D), v[sl].view(n, H, V),
+                                     a[sl].view(n, H, D)).view(n, H * V))
+        at += n
+    want = torch.cat(want)
+    x = dev(proj, dtype)
+    qd, kd, vd = x[:, :H * D], x[:, H * D:2 * H * D], x[:, 2 * H * D:2 * H * D + H * V]
+    state = torch.full((5, H, D, V), 7.0, device="cuda")               # slots hold leftovers until they are zeroed
+    slots = [3, 0, 4]
+    cu = [0, 37, 38, 56]
+    tol = 2e-5 if dtype == "float32" else 1e-5       # the inputs are bfloat16 values on both sides: the arithmetic is float32 either way
+    # whole, as one batch of three entries
+    for s in slots:
+        state[s].zero_()
+    out = torch.empty(T, H * V, device="cuda")
+    ops.gla_scan(out, qd, kd, vd, dev(z), dev(b), tau, D ** -0.5, state, i32(slots), i32(cu), 3)
+    assert max_err(out, want) < tol
+    kept = state.clone()
+    # the same requests cut in two steps, in other slots; the second step is a mixed batch (a decoded token beside portions)
+    for s in (1, 2, 3):
+        state[s].zero_()
+    out2 = torch.full((T, H * V), float("nan"), device="cuda")
+    first = torch.cat([torch.arange(0, 20), torch.arange(38, 40)])
+    rest = torch.cat([torch.arange(20, 37), torch.arange(37, 38), torch.arange(40, 56)])
+    for idx, sl, cu2 in ((first, [1, 2], [0, 20, 22]), (rest, [1, 3, 2], [0, 17, 18, 34])):
+        sub = x[idx.cuda()].contiguous()
+        o = torch.empty(len(idx), H * V, device="cuda")
+        ops.gla_scan(o, sub[:, :H * D], sub[:, H * D:2 * H * D], sub[:, 2 * H * D:2 * H * D + H * V], dev(z[idx]), dev(b), tau,
+                     D ** -0.5, state, i32(sl), i32(cu2), len(sl))
+        out2[idx.cuda()] = o
+    assert max_err(out2, want) < tol
+    assert max_err(state[1], kept[3]) < tol and max_err(state[2], kept[4]) < tol and max_err(state[3], kept[0]) < tol
+
+
+@pytest.mark.parametrize("experts,top", [(1, 1), (4, 2), (7, 7), (12, 3), (37, 5)])
+def test_router_weights_are_shares_of_the_full_softmax(experts, top):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(experts)
+    T, W = 21, 40
+    h, wr = bf(torch.randn(T, W, generator=g)), bf(torch.randn(experts, W, generator=g) * 0.4)
+    logits = torch.empty(T, experts, device="cuda")
+    ids, wts = torch.empty(T * top, dtype=torch.int32, device="cuda"), torch.empty(T * top, device="cuda")
+    ops.moe_route(dev(h), dev(wr), None, logits, ids, wts, T, top, over_all=True)
+    want_ids, want_w = P.route_all(h, wr, top)
+    assert torch.equal(ids.view(T, top).cpu().long(), want_ids)
+    assert max_err(wts.view(T, top), want_w) < 2e-6
+    if top < experts:
+        assert float(wts.view(T, top).sum(1).max()) < 1.0          # not renormalised
+
+
+class _Ctx:
+    def __init__(self, rows, max_rows):
+        from llm_b200.engine.context import Workspace
+        self.n_tokens, self.workspace = rows, Workspace(max_rows, torch.device("cuda"))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("experts,top,ff,rows", [(4, 2, 24, 50), (3, 3, 16, 7), (5, 1, 12, 33), (6, 2, 64, 300), (1, 1, 8, 3)])
+def test_gated_experts_under_the_full_softmax_router(dtype, experts, top, ff, rows):
+    from llm_b200.parts.routed import RoutedFFN
+    g = torch.Generator().manual_seed(experts * 100 + rows)
+    W = 64
+    part = RoutedFFN(W, experts, top, ff, activation="silu", router_bias=False, gated=True, router="softmax_all", prefix="m",
+                     dtype=DT[dtype], device=torch.device("cuda"))
+    w = {"m.router": bf(torch.randn(experts, W, generator=g) * 0.3)}
+    for e in range(experts):
+        w[f"m.e{e}.gate"] = bf(torch.randn(ff, W, generator=g) * 0.2)
+        w[f"m.e{e}.up"] = bf(torch.randn(ff, W, generator=g) * 0.2)
+        w[f"m.e{e}.down"] = bf(torch.randn(W, ff, generator=g) * 0.2)
+    assert set(part.parameters()) == set(w)
+    part.bind({n: dev(t, dtype) for n, t in w.items()})
+    h = bf(torch.randn(rows, W, generator=g))
+    ctx = _Ctx(rows, max(320, rows))
+    out = part.forward(dev(h, dtype), ctx).clone()
+    want = P.moe_ff(h, w["m.router"], top, [tuple(w[f"m.e{e}.{n}"] for n in ("gate", "up", "down")) for e in range(experts)])
+    clear = P.route_margin(h, w["m.router"], top) >= CLOSE_CALL[dtype]
+    assert int(clear.sum()) >= rows // 2
+    assert max_err(out[clear.cuda()], want[clear]) < (1e-5 if dtype == "float32" else 1.5e-2)
+    assert torch.equal(out, part.forward(dev(h, dtype), ctx))        # slots may be dealt differently; the values may not change
+
+
+# ---- whole models, every way of cutting the work --------------------------------------------
+LENGTHS = {"A": [1, 5, 33, 70, 129], "B": [2, 47, 64, 150, 260], "C": [3, 40, 17, 90], "D": [1, 16, 31, 100], "E": [1, 130, 31, 257],
+           "F": [2, 33, 140, 95]}
+
+
+class Ref(torch.Tensor):
+    """Plain logits that also carry, per row, the smallest routing margin of the token."""
+
+
+def plain_with_margin(cfg, w, toks):
+    margins = []
+    ref = P.forward(cfg, w, toks, margins=margins).as_subclass(Ref)
+    ref.margin = torch.stack(margins).min(0).values if margins else torch.full((len(toks),), math.inf, dtype=torch.float64)
+    ref.margin = torch.cummin(ref.margin, dim=0).values          # a close call spoils the rows after it too
+    return ref
+
+
+@pytest.fixture(scope="module")
+def models():
+    cache = {}
+
+    def get(name, dtype="float32"):
+        name = name + ("-all" if dtype.endswith("-all") else "")
+        if name not in cache:
+            cfg, page = CONFIGS[name[0]]
+            if name.endswith("-all"):
+                cfg = every_expert(cfg)
+            w = make_weights(cfg, seed=ord(name[0]), slow=3.0 if name[0] == "E" else 0.0)
+            reqs = {f"r{i}": random_tokens(n, cfg["vocab"], 300 + i) for i, n in enumerate(LENGTHS[name[0]])}
+            ref = {rid: plain_with_margin(cfg, w, toks) for rid, toks in reqs.items()}
+            cache[name] = (cfg, page, w, reqs, ref)
+        return cache[name]
+    return get
+
+
+def compare(got, ref, dtype, what):
+    for rid, r in ref.items():
+        assert got[rid].shape == r.shape, f"{what}: {rid} shape {got[rid].shape} vs {r.shape}"
+        err_rows = (got[rid].double() - r).abs().max(dim=1).values / r.abs().max()
+        margin = getattr(r, "margin", None)
+        if margin is not None:
+            unclear = margin < CLOSE_CALL[dtype]
+            err_rows = torch.where(unclear, torch.zeros_like(err_rows), err_rows)
+        bad = torch.nonzero(err_rows > TOL[dtype])
+        assert bad.numel() == 0, (f"{what}: request {rid} first differs at position {int(bad[0])} "
+                                  f"(err {float(err_rows[int(bad[0])]):.3e}, limit {TOL[dtype]:.1e})")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_every_cut_matches_plain(models, name, dtype):
+    cfg, page, w, reqs, ref = models(name, dtype)
+    longest = max(len(t) for t in reqs.values())
+    eng = make_engine(cfg, w, dtype[:8], page, -(-longest // page) + 1)       # a pool barely larger than the longest request
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, "whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs)), ref, dtype, "tail decode")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs)), ref, dtype, "portions")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs, sizes=(2, 2, 3, 2, 16, 2, 17, 64))), ref, dtype, "small portions")
+    eng.check_status()
+    eng.cache.check()
+    assert all(eng.cache.num_free_pages(g) == eng.cache.group_spec(g).num_pages for g in range(eng.cache.num_groups))
+    lens = sorted((len(t) for t in reqs.values()), reverse=True)
+    eng = make_engine(cfg, w, dtype[:8], page, sum(-(-n // page) for n in lens[:4]) + 1)
+    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, "mixed")     # freed pages and slots are used again
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16-all"])
+def test_batch_of_unequal_requests_equals_each_alone(models, dtype):
+    from llm_b200.engine.engine import StepEntry
+    cfg, page, w, reqs, ref = models("A", dtype)
+    eng = make_engine(cfg, w, dtype[:8], page, 40)
+    alone = replay.run_steps(eng, replay.steps_whole(reqs))
+    entries = [StepEntry(rid, toks, list(range(len(toks)))) for rid, toks in reqs.items() if len(toks) < 129][:4]
+    rows = eng.step(entries).float().cpu()
+    at = 0
+    for e in entries:
+        n = len(e.tokens)
+        clear = ref[e.request_id].margin >= CLOSE_CALL[dtype]
+        assert max_err(rows[at:at + n][clear], alone[e.request_id][clear]) < (1e-5 if dtype == "float32" else 2e-2)
+        at += n
+        eng.release(e.request_id)
+
+
+def test_window_pages_go_back_but_kept_pages_stay(models):
+    """A request far longer than window + kept tokens holds only the pages of both; the logits say they were the right ones."""
+    cfg, page = CONFIGS["D"]                     # window 24, 4 kept tokens, pages of 16
+    w = make_weights(cfg, seed=5)
+    toks = random_tokens(400, cfg["vocab"], 8)
+    ref = {"x": P.forward(cfg, w, toks)}
+    eng = make_engine(cfg, w, "float32", page, 8, max_tokens=48, max_seq_len=512)       # 8 pages: 400 tokens would need 25
+    compare(replay.run_steps(eng, replay.steps_portions({"x": toks}, sizes=(40, 2, 31, 1, 16, 48))), ref, "float32", "portions")
+    eng = make_engine(cfg, w, "float32", page, 4, max_tokens=48, max_seq_len=512)
+    steps = replay.steps_tail_decode({"x": toks[:300]}, tail=299)
+    steps[-1]["end"] = []
+    got = replay.run_steps(eng, steps)             # token by token: kept page + window pages + the one being filled
+    compare(got, {"x": ref["x"][:300]}, "float32", "decode")
+    table = eng.cache.table(0, "x")
+    assert table[0] >= 0 and all(p < 0 for p in table[1:(300 - 24) // page]) and eng.cache.num_free_pages(0) >= 1
+    eng.cache.check()
+
+
+# ---- one key that carries the row: far back, at the window's edges, among the kept tokens ----
+NEEDLE, QUERY = 7, 11
+
+
+def _needle_attention(window, keep, beta=60.0):
+    """One attention layer alone, with the query projection changed so that the token QUERY looks for the token NEEDLE
+    through the channels that do not rotate: Wq += beta * k(NEEDLE) h(QUERY)^T / |h(QUERY)|^2 there.  In the first
+    layer a token's key depends on its id alone (apart from the rotation), so the score of the pair stands out wherever
+    the two are, and is capped at the soft cap; every other score stays small."""
+    cfg = config(64, 120, [layer(attn(2, 1, 32, 16, size=window, keep=keep, rot_dims=8, scale=0.25, softcap=14.0), None)],
+                 mult=1.0, cap=50.0)
+    w = make_weights(cfg, seed=9, peak=0.4)
+    ln = lambda tok: P.layer_norm(w["embed"][tok].double(), w["l0.norm1"], cfg["norm"]["eps"])
+    h_n, h_q = ln(NEEDLE), ln(QUERY)
+    k_n = (w["l0.mix.k"].double() @ h_n)                     # [1 * 32]
+    k_n[:8] = 0.0                                            # the rotating channels take no part
+    k_n = k_n / k_n.norm()
+    add = beta * torch.outer(torch.cat([k_n, k_n]), h_q) / (h_q @ h_q)          # both query heads
+    w["l0.mix.q"] = bf((w["l0.mix.q"].double() + add).float())
+    return cfg, w
+
+
+def _needle_tokens(cfg, n, needles, queries, seed):
+    toks = [t for t in random_tokens(3 * n, cfg["vocab"], seed) if t not in (NEEDLE, QUERY)][:n]
+    for p in needles:
+        toks[p] = NEEDLE
+    for p in queries:
+        toks[p] = QUERY
+    return toks
+
+
+NEEDLE_CASES = {      # name: (window, kept, length, needle positions, query positions [seen], [not seen]); pages hold 16 tokens
+    "window_edge": (24, 0, 200, [100], [101, 112, 123], [124, 125, 160]),
+    "window_edge_at_page_border": (32, 0, 200, [96], [97, 127], [128, 129, 199]),
+    "window_of_one_page": (16, 0, 120, [47], [48, 62], [63, 64, 80]),
+    "kept_token_far_back": (24, 4, 700, [3], [4, 27, 28, 400, 699], []),
+    "first_token_kept": (24, 1, 300, [0], [1, 23, 24, 25, 299], []),
+    "just_past_the_kept": (24, 4, 300, [4], [5, 27], [28, 29, 100, 299]),
+    "kept_beyond_a_page": (8, 20, 200, [19], [20, 27, 28, 150], []),
+    "kept_beyond_a_page_out": (8, 20, 200, [20], [21, 27], [28, 29, 150]),
+    "not_yet_visible": (64, 2, 120, [60], [61, 62, 119], [10, 58, 59]),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", sorted(NEEDLE_CASES))
+def test_one_key_carries_the_row(dtype, case):
+    window, keep, n, needles, seen, unseen = NEEDLE_CASES[case]
+    cfg, w = _needle_attention(window, keep)
+    toks = _needle_tokens(cfg, n, needles, seen + unseen, seed=len(case))
+    ref = P.forward(cfg, w, toks)
+    blind = list(toks)
+    for p in needles:
+        blind[p] = 3
+    other = P.forward(cfg, w, blind)
+    gap = (ref - other).abs().max(dim=1).values / ref.abs().max()
+    # the test's premise: the needle moves the logits where it is seen, and nowhere else among the queries
+    assert float(gap[seen].min()) > 2.5 * TOL[dtype], f"the needle does not stand out ({float(gap[seen].min()):.2e})"
+    if unseen:
+        assert float(gap[unseen].max()) < 1e-9
+    reqs, refs = {"n": toks}, {"n": ref}
+    page = 16
+    eng = make_engine(cfg, w, dtype, page, -(-n // page) + 2, max_tokens=768)
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), refs, dtype, "whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs, tail=min(n - 1, 190))), refs, dtype, "decode")
+    compare(replay.run_steps(eng, replay.steps_portions(reqs, sizes=(2, 14, 1, 16, 3, 29, 2, 64, 5))), refs, dtype, "portions")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_state_remembers_a_token_from_hundreds_back(dtype):
+    """A gla layer alone with decays close to one: what token NEEDLE wrote into the state is read 600 tokens later by
+    QUERY, through portions, decoded tokens and a state slot that another request used before."""
+    cfg = config(48, 150, [layer(gla(2, 24, 16, tau=32.0), None)], mult=1.0, cap=60.0)
+    w = make_weights(cfg, seed=21, slow=6.0)
+    ln = lambda tok: P.layer_norm(w["embed"][tok].double(), w["l0.norm1"], cfg["norm"]["eps"])
+    k_n = w["l0.mix.k"].double() @ ln(NEEDLE)
+    h_q = ln(QUERY)
+    w["l0.mix.q"] = bf((w["l0.mix.q"].double() + 40.0 * torch.outer(k_n / k_n.norm(), h_q) / (h_q @ h_q)).float())
+    toks = _needle_tokens(cfg, 700, [50], [51, 300, 650, 699], seed=4)
+    ref = P.forward(cfg, w, toks)
+    blind = list(toks)
+    blind[50] = 3
+    gap = (ref - P.forward(cfg, w, blind)).abs().max(dim=1).values / ref.abs().max()
+    # the premise: what was written 650 tokens ago still moves the logits (a linear memory has no softmax to make one
+    # key stand out, so the bound is modest; a state that is lost on the way moves them by far more)
+    assert float(gap[[51, 300, 650, 699]].min()) > 5e-3
+    eng = make_engine(cfg, w, dtype, 16, 4, max_tokens=768, max_seqs=1, max_seq_len=1024)
+    other = {"o": random_tokens(90, cfg["vocab"], 1)}
+    replay.run_steps(eng, replay.steps_whole(other))                      # leaves its state in the only slot
+    compare(replay.run_steps(eng, replay.steps_whole({"n": toks})), {"n": ref}, dtype, "whole")
+    compare(replay.run_steps(eng, replay.steps_portions({"n": toks}, sizes=(2, 49, 1, 250, 3, 64))), {"n": ref}, dtype, "portions")
+    compare(replay.run_steps(eng, replay.steps_tail_decode({"n": toks}, tail=400)), {"n": ref}, dtype, "decode")
+
+
+# ---- long decoding and generation through the scheduler --------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16-all"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decode_with_graphs_and_first_tokens(models, name, dtype):
+    from llm_b200.engine.engine import StepEntry
+    cfg, page, w, _reqs, _ref = models(name, dtype)
+    toks = random_tokens(210, cfg["vocab"], 77)
+    ref = plain_with_margin(cfg, w, toks)
+    eng = make_engine(cfg, w, dtype[:8], page, -(-210 // page) + 1, max_tokens=64, max_seqs=2, poison=False, graphs=True)
+    rows = [eng.step([StepEntry("x", toks[:2], [0, 1])]).double().cpu().clone()]
+    for t in toks[2:]:
+        rows.append(eng.step([StepEntry("x", [t], [0])]).double().cpu().clone())
+    eng.check_status()
+    compare({"x": torch.cat(rows)}, {"x": ref}, dtype, "long decode")
+    assert eng.counters["graph_replays"] > 100
+
+
+def _plain_greedy(cfg, w, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(torch.argmax(P.forward(cfg, w, ids)[-1])))
+    return ids[len(prompt):]
+
+
+def test_greedy_generation_through_the_scheduler(models):
+    from llm_b200 import LLM
+    cfg, page, w, _reqs, _ref = models("A")
+    prompts = [random_tokens(n, cfg["vocab"], 500 + n) for n in (1, 9, 30, 47, 18)]
+    llm = LLM(None, dtype="float32", max_num_seqs=3, max_num_batched_tokens=16, kv_block_size=page, num_kv_blocks=14,
+              eos_token_id=-1, random_config=cfg, tensors={k: v.clone() for k, v in w.items()}, max_seq_len=128)
+    got = llm.generate(prompts, max_new_tokens=20)
+    for p, g in zip(prompts, got):
+        assert g == _plain_greedy(cfg, w, p, 20)
+    llm.engine.cache.check()
+
+
+def test_trace_replay_of_a_folder(models, tmp_path):
+    """A model folder written to disk (bfloat16 matrices, a decay rank that only the file knows) and replayed through
+    the trace runner's entry point."""
+    import io
+    import json
+    import numpy as np
+    from llm_b200.engine import trace
+    from llm_b200.weights.safetensors_io import write_safetensors
+    cfg, page, w, reqs, ref = models("A")
+    d = tmp_path / "model"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(d / "model.safetensors"), {k: v.to(torch.bfloat16) for k, v in w.items()})
+    lines, want = [], {}
+    for n, st in enumerate(replay.steps_mixed({k: v for k, v in reqs.items() if len(v) > 1})):
+        lines.append(json.dumps({"step": n, **st}))
+        want[n] = [(e["id"], len(e["want"])) for e in st["entries"]]
+    out = io.StringIO()
+    assert trace.main(["--model", str(d), "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "512"],
+                      stdin=io.StringIO("\n".join(lines) + "\n"), stdout=out) == 0
+    assert out.getvalue().split() == [x for n in range(len(lines)) for x in ("done", str(n))]
+    at = {rid: 0 for rid in reqs}
+    for n, rows in want.items():
+        got = torch.from_numpy(np.fromfile(tmp_path / "o" / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"]).copy())
+        r = 0
+        for rid, k in rows:
+            assert max_err(got[r:r + k], ref[rid][at[rid]:at[rid] + k]) < 1e-4
+            at[rid] += k
+            r += k
+
+
+# ---- seeded random configurations -----------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", range(10))
+def test_seeded_random_configurations(seed, dtype):
+    cfg = random_config(2000 + seed)
+    if dtype.endswith("-all"):
+        cfg = every_expert(cfg)
+    w = make_weights(cfg, seed=seed, peak=1.0, decay_rank=[3, 8, 16][seed % 3])
+    page = [8, 16, 32][seed % 3]
+    reqs = {f"r{i}": random_tokens(n, cfg["vocab"], 40 + i) for i, n in enumerate([3, 45, 70, 131])}
+    ref = {rid: plain_with_margin(cfg, w, toks) for rid, toks in reqs.items()}
+    eng = make_engine(cfg, w, dtype[:8], page, sum(-(-len(t) // page) for t in reqs.values()) + 1)
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, f"seed {seed} whole")
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs, tail=20)), ref, dtype, f"seed {seed} tail decode")
+    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, f"seed {seed} mixed")
+    eng.cache.check()
