@@ -396,9 +396,36 @@ DESIGN_SIZES = {
 }
 
 
-def design_comparison(args, peaks) -> int:
-    """Prefill and decode throughput of Tevudra beside Llama at equal layer sizes (random weights, bfloat16), with
-    the device time of every kernel of one prompt step and one decode step.  One JSON line per size."""
+def fopivik_config(width, layers, heads, kv_heads, dim, window, gla_heads, gla_dim, gla_vdim, experts, top, expert_ff,
+                   vocab=32000):
+    """Layers alternate between the windowed sink attention and the gated linear attention, each with a mixture of gated
+    experts; the first two layers run twice."""
+    ls = []
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                     "mask": {"size": window, "keep_first": 4},
+                     "rot": {"dims": dim // 2, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            ls.append({"type": "attention", "mixer": mixer, "mlp": moe})
+        else:
+            ls.append({"type": "gla", "mixer": {"heads": gla_heads, "dim": gla_dim, "vdim": gla_vdim, "tau": 16.0}, "mlp": moe})
+    return {"architecture": "Fopivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+            "logit_softcap": 30.0, "layers": ls, "loop": {"start": 0, "stop": 2, "times": 2}, "max_position": 4096}
+
+
+# name -> (Fopivik config, Llama config of the same width and heads; Llama's depth equals Fopivik's layer runs, and its
+# feed-forward the experts a token uses: top x expert_ff)
+FOPIVIK_SIZES = {
+    "2048": (fopivik_config(2048, 6, 16, 4, 128, 1024, 8, 128, 256, 16, 4, 1408), llama_config(2048, 8, 16, 4, 128, 5632)),
+    "4096": (fopivik_config(4096, 2, 32, 8, 128, 1024, 16, 128, 256, 32, 4, 2752), llama_config(4096, 4, 32, 8, 128, 11008)),
+    "1024-head64": (fopivik_config(1024, 6, 16, 4, 64, 512, 8, 64, 128, 8, 2, 1408), llama_config(1024, 8, 16, 4, 64, 2816)),
+}
+
+
+def design_comparison(args, peaks, design: str = "tevudra") -> int:
+    """Prefill and decode throughput of a design (Tevudra or Fopivik) beside Llama at equal layer sizes (random weights,
+    bfloat16), with the device time of every kernel of one prompt step and one decode step.  One JSON line per size."""
     import collections
 
     import numpy as np
@@ -476,13 +503,14 @@ def design_comparison(args, peaks) -> int:
         torch.cuda.empty_cache()
         return out
 
-    sizes = [s for s in DESIGN_SIZES if not args.sizes or s in args.sizes.split(",")]
+    table = FOPIVIK_SIZES if design == "fopivik" else DESIGN_SIZES
+    sizes = [s for s in table if not args.sizes or s in args.sizes.split(",")]
     for name in sizes:
-        tev, lla = DESIGN_SIZES[name]
+        tev, lla = table[name]
         sampler = ClockSampler()
         sampler.start()
-        res = {"mode": "tevudra", "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids",
-               "tevudra": measure(tev), "llama": measure(lla), "peaks": peaks}
+        res = {"mode": design, "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids",
+               design: measure(tev), "llama": measure(lla), "peaks": peaks}
         res["clocks"] = sampler.stop()
         print(json.dumps(res), flush=True)
     return 0
@@ -500,14 +528,14 @@ def main() -> int:
     ap.add_argument("--no-shapes", action="store_true",
                     help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
     ap.add_argument("--mode", default="all",
-                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention", "tevudra"],
+                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention", "tevudra", "fopivik"],
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line); "
                          "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph; "
                          "decode_attention: the decode attention kernel alone over batches and context lengths "
                          "(--batch with --ctx: that one case); "
-                         "tevudra: the Tevudra design beside Llama at equal layer sizes, prompt and decode, with every kernel's time")
+                         "tevudra, fopivik: that design beside Llama at equal layer sizes, prompt and decode, with every kernel's time")
     ap.add_argument("--latent", action="store_true", help="decode_attention: the key pages are the value pages too")
-    ap.add_argument("--sizes", default="", help="tevudra: which of the sizes to run (comma-separated; default all)")
+    ap.add_argument("--sizes", default="", help="tevudra, fopivik: which of the sizes to run (comma-separated; default all)")
     ap.add_argument("--ctx", type=int, default=0, help="decode_attention: the context length of the one case to run")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="timeline_prefill: tokens of the prompt step")
     ap.add_argument("--heads", default="32,4,64", help="decode_attention: query heads, kv heads, head size")
@@ -530,8 +558,8 @@ def main() -> int:
     peaks = load_peaks()
     if args.mode == "decode_attention":
         return decode_attention_sweep(args, peaks, torch, ops)
-    if args.mode == "tevudra":
-        return design_comparison(args, peaks)
+    if args.mode in ("tevudra", "fopivik"):
+        return design_comparison(args, peaks, args.mode)
     cfg = dict(MODEL, num_hidden_layers=args.layers)
     if args.mode != "all":
         args.no_points = True

@@ -13,6 +13,9 @@
 // The reference runs decode through its prefill kernel, one 16-row MMA tile per head with
 // one row used and no split (kernel/attention/attention_NH_32_NKV_4_HS_64.h:374-386).
 // Softmax and all sums are float32; visible keys are max(0, pos-window+1) .. pos.
+// Options as in the general kernel: a soft cap on the scaled scores, a sink (one more term of score 0
+// in the denominator, added when the ranges are merged), and, with a window, the request's first
+// keep_first keys, which stay visible: the ranges then run over the kept keys followed by the window's.
 #include "common.cuh"
 
 namespace {
@@ -60,7 +63,7 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
                         const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
                         const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ kv_lens, int n_heads, int n_kv, int head_dim_arg, int page_size,
-                        int window, float scale, int splits) {
+                        int window, float scale, int splits, float softcap, int sink, int keep_first) {
   constexpr bool STAGE_V = HS > 0;
   constexpr int QW = HS > 0 ? HS : MAX_HS;
   constexpr int V_PITCH = HS + 16 / (int)sizeof(T);                 // elements; rows stay 16-byte aligned
@@ -94,11 +97,15 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
   }
   const int pos = n_held - 1;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int n_keys = pos - lo + 1;
+  // visible keys in the order they are walked: [0, keep_end) and then [lo, pos]; index u of that list is key
+  // u (u < keep_end) or u + skip
+  const int keep_end = min(keep_first, lo), skip = lo - keep_end;
+  const int n_keys = keep_end + pos - lo + 1;
   int chunk = (n_keys + splits - 1) / splits;
   chunk = (chunk + SUB - 1) / SUB * SUB;        // whole rounds
-  const int k_begin = lo + split * chunk;
-  const int k_end = min(pos + 1, k_begin + chunk);
+  const int k_begin = split * chunk;
+  const int k_end = min(n_keys, k_begin + chunk);
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   const int* table = block_table + (size_t)e * table_width;
   const int n_dp = head_dim / 2;                 // pairs of output dims
   const int n_kg = THREADS / n_dp;               // key groups in the value phase
@@ -134,7 +141,7 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
       const int key = tid / KT, part = tid % KT;
       const bool has_key = key < n_sub;
       if (has_key) {
-        const int kp = base + key;
+        const int u = base + key, kp = u < keep_end ? u : u + skip;
         const long long row = (((long long)table[kp / page_size] * n_kv + g) * page_size + kp % page_size) * head_dim;
         if (part == 0) row_s[key] = row;
         if (STAGE_V) {
@@ -185,6 +192,7 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
       for (int h = 0; h < GT; ++h) {                 // the KT threads of a key are neighbouring lanes
         s[h] += __shfl_xor_sync(0xffffffffu, s[h], 1);
         s[h] += __shfl_xor_sync(0xffffffffu, s[h], 2);
+        if (softcap > 0.f) s[h] = softcap * tanhf(s[h] * inv_cap);
         if (!has_key) s[h] = -INFINITY;
       }
       // ---- running maximum per head over the CTA ----
@@ -286,7 +294,11 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
     if (splits == 1) {
       for (int i = tid; i < nh * head_dim; i += THREADS) {
         const int h = i / head_dim, d = i % head_dim;
-        out[(size_t)e * out_stride + (size_t)(head0 + h) * head_dim + d] = from_f32<T>(o_sum[i] / l_s[h]);
+        // the sink joins the denominator with weight exp(0 - m); above m = 0 the row is rescaled to it first
+        const float m_ref = sink ? fmaxf(m_s[h], 0.f) : m_s[h];
+        const float w = sink ? expf(m_s[h] - m_ref) : 1.f;
+        const float denom = l_s[h] * w + (sink ? expf(-m_ref) : 0.f);
+        out[(size_t)e * out_stride + (size_t)(head0 + h) * head_dim + d] = from_f32<T>(o_sum[i] * w / denom);
       }
     } else {
       for (int i = tid; i < nh * head_dim; i += THREADS) {
@@ -327,9 +339,9 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
     }
     __syncthreads();
     if (tid < nh) {                                                     // weights exp(m_s - m) / l, from shared memory only
-      float m = -INFINITY;
+      float m = sink ? 0.f : -INFINITY;               // the sink is one more range: maximum 0, sum 1, no values
       for (int sp = 0; sp < n_active; ++sp) m = fmaxf(m, w_s[tid * splits + sp]);
-      float l = 0.f;
+      float l = sink ? expf(-m) : 0.f;
       for (int sp = 0; sp < n_active; ++sp) {
         const float wgt = expf(w_s[tid * splits + sp] - m);
         l += wgt * l_in[tid * splits + sp];
@@ -374,8 +386,11 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
                                          const void* k_pages, const void* v_pages, const int* block_table,
                                          int table_width, const int* kv_lens, int n_entries, int n_heads, int n_kv,
                                          int head_dim, int page_size, int window, float scale, int splits,
-                                         float* scratch, int dtype, cudaStream_t stream) {
+                                         float* scratch, int dtype, cudaStream_t stream, float softcap, int sink,
+                                         int keep_first) {
   if (n_entries == 0) return 0;
+  LLMK_REQUIRE(softcap >= 0.f && keep_first >= 0, "attention_decode: bad soft cap %f or keep_first %d", (double)softcap, keep_first);
+  if (window == 0) keep_first = 0;
   LLMK_REQUIRE(head_dim > 0 && head_dim % 16 == 0 && head_dim <= MAX_HS,
                "attention_decode: head_dim %d must be a multiple of 16 up to %d", head_dim, MAX_HS);
   LLMK_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads", n_heads, n_kv);
@@ -392,7 +407,7 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
     if (head_dim == 128) kern = decode_attention_kernel<T, 128>;
     launch_kernel(kern, grid, dim3(THREADS), 0, stream, (T*)out, out_stride, scratch, (const T*)q, q_stride,
                   (const T*)k_pages, (const T*)v_pages, block_table, table_width, kv_lens, n_heads, n_kv, head_dim,
-                  page_size, window, scale, splits);
+                  page_size, window, scale, splits, softcap, sink, keep_first);
     LLMK_LAUNCH_CHECK("attention_decode");
   });
 }
@@ -446,5 +461,5 @@ LLMK_API int llmk_paged_attention_decode_static(void* out, long long out_stride,
   if (rc) return rc;
   return llmk_paged_attention_decode(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, kv_lens,
                                      n_entries, n_heads, n_kv, head_dim, page_size, window, scale, splits, scratch,
-                                     dtype, stream);
+                                     dtype, stream, 0.f, 0, 0);
 }

@@ -243,12 +243,19 @@ def rope_pairs_kv_write(qkv, freqs, positions: torch.Tensor, slot_map, k_pages, 
 
 
 def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias, tau: float,
-             q_scale: float, state: torch.Tensor, state_slots: torch.Tensor, cu_tokens: torch.Tensor, n_entries: int) -> None:
+             q_scale: float, state: torch.Tensor, state_slots: torch.Tensor, cu_tokens: torch.Tensor, n_entries: int,
+             n_tokens: int = 0, seg_len: int = 0, seg_state=None, seg_decay=None) -> None:
     """The gated-linear-attention recurrence over every entry's tokens (see recurrent.cu): q, k [T, heads*dim] and
     v [T, heads*vdim] are column ranges of one projection (equal row strides), z float32 [T, heads*dim] the decay's
     pre-activation (+ z_bias), state float32 [slots, heads, dim, vdim] read and written at state_slots[entry],
-    out float32 [T, heads*vdim]."""
+    out float32 [T, heads*vdim].  seg_len > 0: entries run as segments of that many tokens side by side, in two passes;
+    n_tokens is the step's token count and seg_state / seg_decay are float32 scratch for n_tokens // seg_len + n_entries
+    segments ([.., heads, dim, vdim] and [.., heads, dim])."""
     heads, dim, vdim = state.shape[1], state.shape[2], state.shape[3]
+    if seg_len:
+        segs = n_tokens // seg_len + n_entries
+        assert seg_state.dtype == seg_decay.dtype == torch.float32 and seg_state.is_contiguous() and seg_decay.is_contiguous()
+        assert seg_state.numel() >= segs * heads * dim * vdim and seg_decay.numel() >= segs * heads * dim
     for t in (q, k, v, z, out):
         _rows_contig(t, "gla operand")
     assert q.stride(0) == k.stride(0) == v.stride(0) and q.dtype == k.dtype == v.dtype
@@ -259,7 +266,9 @@ def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     _check(load().llmk_gla_scan(_ptr(out), c_longlong(out.stride(0)), _ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), _ptr(z),
                                 c_longlong(z.stride(0)), _ptr(z_bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(state_slots),
                                 _ptr(cu_tokens), c_int(n_entries), c_int(heads), c_int(dim), c_int(vdim), c_int(_kind(q.dtype)),
-                                _stream()))
+                                _stream(), c_int(n_tokens), c_int(seg_len), _ptr(seg_state), _ptr(seg_decay)))
+    if seg_len:
+        count_launches(2)
 
 
 ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
@@ -567,9 +576,11 @@ def decode_splits(n_entries: int, n_kv: int, max_keys: int, sms: int = 0) -> int
 
 def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                            block_table: torch.Tensor, kv_lens: torch.Tensor, n_entries: int, n_heads: int,
-                           n_kv: int, head_dim: int, window: int, scale: float, splits=None, max_keys: int = 0) -> None:
+                           n_kv: int, head_dim: int, window: int, scale: float, splits=None, max_keys: int = 0,
+                           softcap: float = 0.0, sink: bool = False, keep_first: int = 0) -> None:
     """One query token per entry (row e of q), attending to its request's kv_lens[e] keys.
-    max_keys: an upper bound of kv_lens, if the host knows one below the table's width."""
+    max_keys: an upper bound of kv_lens, if the host knows one below the table's width.
+    softcap, sink, keep_first: as in paged_attention_generic (the CUDA-core kernel takes them)."""
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert kv_lens.dtype == torch.int32 and k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -584,11 +595,13 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
             c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)))
     # bfloat16 with a head size of 64 or 128 and pages of a power of two: the query heads of a
     # group as rows of warp-level MMAs (tensor-core library); everything else on the CUDA cores
-    if (q.dtype == torch.bfloat16 and head_dim in (64, 128) and page & (page - 1) == 0
+    extended = bool(softcap or sink or keep_first)
+    if (not extended and q.dtype == torch.bfloat16 and head_dim in (64, 128) and page & (page - 1) == 0
             and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0):
         _check_t(load_tensor().llmk_paged_attention_decode_mma(*args, c_int(max_keys), _stream()))
     else:
-        _check(load().llmk_paged_attention_decode(*args, _stream()))
+        _check(load().llmk_paged_attention_decode(*args, _stream(), c_float(softcap or 0.0), c_int(int(bool(sink))),
+                                                  c_int(keep_first or 0)))
 
 
 def _decode_scratch_floats(n_entries: int, n_heads: int, head_dim: int, splits: int) -> int:
@@ -674,7 +687,19 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     where it takes the sizes; the general kernel for float32 and for all other sizes (head sizes
     off the 16-grid among them).  value_dim, softcap, sink, keep_first: see paged_attention_generic, the kernel
     that takes them in every combination."""
-    if (value_dim and value_dim != head_dim) or softcap or sink or keep_first:
+    extended = bool((value_dim and value_dim != head_dim) or softcap or sink or keep_first)
+    if (extended and ctx.decode_only and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
+            and (not value_dim or value_dim == head_dim)):
+        # single tokens: the split-key kernel (CUDA cores) takes the soft cap, the sink and the kept keys
+        max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
+        if window:
+            max_keys = min(max_keys, window + keep_first)
+        paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
+                               n_heads, n_kv, head_dim, window, scale,
+                               splits=decode_splits(ctx.n_entries, n_kv, max_keys), max_keys=max_keys,
+                               softcap=softcap, sink=sink, keep_first=keep_first)
+        return
+    if extended:
         paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                                 ctx.n_tokens, n_heads, n_kv, head_dim, window, scale, value_dim=value_dim,
                                 softcap=softcap, sink=sink, keep_first=keep_first)

@@ -15,6 +15,15 @@
 // CHUNK at a time (q, k, a once per CTA, broadcast to the threads of a row group); each thread
 // updates its rows and keeps a partial o per token, and the partial sums of the row groups are
 // added in the order of g after every chunk.
+//
+// Long entries (prompts) are cut into segments of seg_len tokens that run side by side, since one
+// entry alone offers only heads x vdim x dim / 16 threads: pass 1 walks every segment from a zero
+// state and keeps its end state L and the product A of its decays; a small kernel chains them,
+// S_start(s + 1) = diag(A_s) S_start(s) + L_s, from the request's state, which it also brings up to
+// date; pass 2 walks every segment again from its true start state and writes the outputs.  This
+// regroups the float32 sums of the recurrence (a token's result then depends, within rounding, on
+// where its segment begins); entries of up to seg_len tokens, decoded tokens among them, are one
+// segment and take the single pass.
 #include "common.cuh"
 
 namespace {
@@ -30,10 +39,14 @@ __global__ void __launch_bounds__(VT * MAX_GROUPS)
 gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restrict__ q, const T* __restrict__ k,
                 const T* __restrict__ v, long long qkv_stride, const float* __restrict__ z, long long z_stride,
                 const float* __restrict__ z_bias, float inv_tau, float q_scale, float* __restrict__ state,
-                const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, int heads, int dim, int vdim) {
+                const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, int heads, int dim, int vdim,
+                int seg_len, int max_segs, int mode, float* __restrict__ seg_state, float* __restrict__ seg_decay) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
+  // mode 0: the whole entry from its request's state, which is written back.  mode 1 (pass 1 of a segmented run):
+  // a segment from zero, no outputs; its end state and decay product go to seg_state / seg_decay.  mode 2 (pass 2):
+  // a segment from seg_state (by then its true start), outputs only.
   const int groups = blockDim.y, dpad = groups * ROWS;
   float* q_s = smem;                          // [CHUNK][dpad]
   float* k_s = q_s + CHUNK * dpad;
@@ -42,16 +55,26 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
   float* part = v_s + CHUNK * VT;             // [CHUNK][groups][VT]
   const int j = threadIdx.x, g = threadIdx.y;
   const int tid = g * VT + j, nthreads = VT * groups;
-  const int entry = blockIdx.z, head = blockIdx.y, col = blockIdx.x * VT + j;
-  const int t0 = cu_tokens[entry], t1 = cu_tokens[entry + 1];
-  float* S_g = state + (((size_t)state_slots[entry] * heads + head) * dim) * vdim;
+  const int entry = blockIdx.z / max_segs, seg = blockIdx.z % max_segs, head = blockIdx.y, col = blockIdx.x * VT + j;
+  int t0 = cu_tokens[entry], t1 = cu_tokens[entry + 1];
+  size_t seg_index = 0;
+  if (mode != 0) {
+    if (seg * seg_len >= t1 - t0) return;
+    for (int e = 0; e < entry; ++e) seg_index += (cu_tokens[e + 1] - cu_tokens[e] + seg_len - 1) / seg_len;
+    seg_index += seg;
+    t0 += seg * seg_len;
+    t1 = min(t1, t0 + seg_len);
+  }
+  float* S_g = mode == 0 ? state + (((size_t)state_slots[entry] * heads + head) * dim) * vdim
+                         : seg_state + ((seg_index * heads + head) * dim) * vdim;
   const bool col_ok = col < vdim;
 
-  float S[ROWS];
+  float S[ROWS], A[ROWS];
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
     const int d = g * ROWS + i;
-    S[i] = (col_ok && d < dim) ? S_g[(size_t)d * vdim + col] : 0.f;
+    S[i] = (mode != 1 && col_ok && d < dim) ? S_g[(size_t)d * vdim + col] : 0.f;
+    A[i] = 1.f;
   }
   for (int c0 = t0; c0 < t1; c0 += CHUNK) {
     const int n = min(CHUNK, t1 - c0);
@@ -79,6 +102,14 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
       const float* kc = k_s + c * dpad + g * ROWS;
       const float* ac = a_s + c * dpad + g * ROWS;
       float o = 0.f;
+      if (mode == 1) {
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+          S[i] = fmaf(ac[i], S[i], kc[i] * vv);
+          A[i] *= ac[i];
+        }
+        continue;
+      }
 #pragma unroll
       for (int i = 0; i < ROWS; ++i) {
         S[i] = fmaf(ac[i], S[i], kc[i] * vv);
@@ -86,6 +117,7 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
       }
       part[(c * groups + g) * VT + j] = o;
     }
+    if (mode == 1) continue;
     __syncthreads();
     for (int idx = tid; idx < n * VT; idx += nthreads) {
       const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
@@ -95,11 +127,39 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
       out[(size_t)(c0 + c) * out_stride + (size_t)head * vdim + cc] = o;
     }
   }
+  if (mode == 2) return;
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) {
     const int d = g * ROWS + i;
     if (col_ok && d < dim) S_g[(size_t)d * vdim + col] = S[i];
+    if (mode == 1 && blockIdx.x == 0 && j == 0 && d < dim) seg_decay[(seg_index * heads + head) * dim + d] = A[i];
   }
+}
+
+// Chains the segments of every entry: seg_state[s] holds the segment's end state from zero on entry and its true start
+// state on exit; the request's state moves to the end of the entry.  One thread per element of the state.
+__global__ void gla_chain_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_decay, float* __restrict__ state,
+                                 const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, int heads, int dim,
+                                 int vdim, int seg_len) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int entry = blockIdx.y;
+  const size_t per = (size_t)heads * dim * vdim;
+  const size_t el = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (el >= per) return;
+  size_t seg0 = 0;
+  for (int e = 0; e < entry; ++e) seg0 += (cu_tokens[e + 1] - cu_tokens[e] + seg_len - 1) / seg_len;
+  const int n_seg = (cu_tokens[entry + 1] - cu_tokens[entry] + seg_len - 1) / seg_len;
+  const size_t row = el / vdim;                       // (head, d)
+  float* S_g = state + (size_t)state_slots[entry] * per + el;
+  float S = *S_g;
+  for (int s = 0; s < n_seg; ++s) {
+    float* at = seg_state + (seg0 + s) * per + el;
+    const float local = *at;
+    *at = S;
+    S = fmaf(seg_decay[(seg0 + s) * heads * dim + row], S, local);
+  }
+  *S_g = S;
 }
 
 }  // namespace
@@ -110,30 +170,49 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
 // [slots, heads, dim, vdim]; state_slots [entries]; cu_tokens [entries + 1]: entry e owns tokens cu[e] .. cu[e+1]-1.
 // A launch that 32 columns a tile would leave with fewer CTAs than SMs takes narrower tiles (16, 8); the sums of
 // a column do not depend on the tile's width.
+// seg_len > 0: entries run as segments of seg_len tokens in two passes (see the head of the file); n_tokens is then the
+// step's number of tokens, seg_state float32 [n_tokens / seg_len + n_entries, heads, dim, vdim] and seg_decay
+// [same, heads, dim] scratch.  seg_len 0: one pass.
 LLMK_API int llmk_gla_scan(float* out, long long out_stride, const void* q, const void* k, const void* v,
                            long long qkv_stride, const float* z, long long z_stride, const float* z_bias, float tau,
                            float q_scale, float* state, const int* state_slots, const int* cu_tokens, int n_entries,
-                           int heads, int dim, int vdim, int dtype, cudaStream_t stream) {
+                           int heads, int dim, int vdim, int dtype, cudaStream_t stream, int n_tokens, int seg_len,
+                           float* seg_state, float* seg_decay) {
   if (n_entries == 0) return 0;
+  LLMK_REQUIRE(seg_len >= 0 && (seg_len == 0 || (seg_state && seg_decay && n_tokens > 0)), "gla_scan: segments need their scratch");
+  // the longest entry has at most n_tokens - (n_entries - 1) tokens: a bound that depends on the step's sizes alone
+  const int max_segs = seg_len ? (n_tokens - (n_entries - 1) + seg_len - 1) / seg_len : 1;
+  LLMK_REQUIRE((long long)n_entries * max_segs <= 65535, "gla_scan: too many segments for one launch");
   LLMK_REQUIRE(heads > 0 && dim > 0 && vdim > 0, "gla_scan: sizes must be positive");
   LLMK_REQUIRE(dim <= ROWS * MAX_GROUPS, "gla_scan: key size %d exceeds %d", dim, ROWS * MAX_GROUPS);
   LLMK_REQUIRE(tau > 0.f, "gla_scan: tau must be positive");
   LLMK_REQUIRE(n_entries <= 65535 && heads <= 65535, "gla_scan: too many entries or heads for one launch");
   const int groups = (dim + ROWS - 1) / ROWS;
-  const long long wide = (long long)((vdim + 31) / 32) * heads * n_entries;
+  const long long wide = (long long)((vdim + 31) / 32) * heads * n_entries * (seg_len ? (n_tokens + seg_len - 1) / seg_len : 1);
   const int sms = llmk_sm_count();
   const int vt = wide >= sms ? 32 : (wide * 2 >= sms ? 16 : 8);
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
-    auto launch = [&](auto kern, int VT) {
+    auto launch = [&](auto kern, int VT, int mode) {
       const size_t smem = sizeof(float) * ((size_t)CHUNK * groups * ROWS * 3 + (size_t)CHUNK * VT + (size_t)CHUNK * groups * VT);
-      return launch_kernel(kern, dim3((vdim + VT - 1) / VT, heads, n_entries), dim3(VT, groups), smem, stream, out, out_stride,
-                           (const T*)q, (const T*)k, (const T*)v, qkv_stride, z, z_stride, z_bias, 1.f / tau, q_scale, state,
-                           state_slots, cu_tokens, heads, dim, vdim);
+      return launch_kernel(kern, dim3((vdim + VT - 1) / VT, heads, n_entries * max_segs), dim3(VT, groups), smem, stream, out,
+                           out_stride, (const T*)q, (const T*)k, (const T*)v, qkv_stride, z, z_stride, z_bias, 1.f / tau, q_scale,
+                           state, state_slots, cu_tokens, heads, dim, vdim, seg_len, max_segs, mode, seg_state, seg_decay);
     };
-    if (vt == 32) launch(gla_scan_kernel<T, 32>, 32);
-    else if (vt == 16) launch(gla_scan_kernel<T, 16>, 16);
-    else launch(gla_scan_kernel<T, 8>, 8);
+    auto pass = [&](int mode) {
+      if (vt == 32) launch(gla_scan_kernel<T, 32>, 32, mode);
+      else if (vt == 16) launch(gla_scan_kernel<T, 16>, 16, mode);
+      else launch(gla_scan_kernel<T, 8>, 8, mode);
+    };
+    if (seg_len == 0) {
+      pass(0);
+    } else {
+      pass(1);
+      const size_t per = (size_t)heads * dim * vdim;
+      launch_kernel(gla_chain_kernel, dim3((unsigned)((per + 255) / 256), n_entries), dim3(256), 0, stream, seg_state,
+                    (const float*)seg_decay, state, state_slots, cu_tokens, heads, dim, vdim, seg_len);
+      pass(2);
+    }
     LLMK_LAUNCH_CHECK("gla_scan");
   });
 }

@@ -23,6 +23,9 @@ _NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "norm": "norm",
           "decay_bias": "a2.b"}
 
 
+SEGMENT = 64       # tokens per segment of a prompt step (see csrc/recurrent.cu)
+
+
 class GatedLinearAttention(Part):
     role = "mixer"
 
@@ -78,8 +81,15 @@ class GatedLinearAttention(Part):
         # the decay's pre-activation in float32; bias, log-sigmoid and the power are the recurrence kernel's
         z = linear(low, self.w_decay, ws.get("gla_decay", T, QK, torch.float32), T)
         o = ws.get("gla_o", T, VS, torch.float32)
+        # a step with prompt portions runs them as segments side by side (two passes); single tokens take one pass
+        seg = 0 if (ctx.decode_only or T < 4 * SEGMENT) else SEGMENT
+        seg_state = seg_decay = None
+        if seg:
+            cap = ws.max_rows // seg + ctx.cu_tokens.numel()
+            seg_state = ws.flat("gla_seg_state", cap * self.num_heads * self.head_dim * self.value_dim, torch.float32)
+            seg_decay = ws.flat("gla_seg_decay", cap * self.num_heads * self.head_dim, torch.float32)
         ops.gla_scan(o, q, k, v, z, self.b_decay, self.tau, self.head_dim ** -0.5, view.state, ctx.state_slots,
-                     ctx.cu_tokens, ctx.n_entries)
+                     ctx.cu_tokens, ctx.n_entries, n_tokens=T, seg_len=seg, seg_state=seg_state, seg_decay=seg_decay)
         normed = ws.get("attn_out", T, VS, self.dtype)
         ops.head_rmsnorm_gate(normed, o, self.gain, gate, T, self.num_heads, self.eps)
         return linear(normed, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)

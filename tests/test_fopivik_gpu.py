@@ -251,6 +251,63 @@ def test_gla_recurrence_whole_cut_and_in_reused_slots(dtype, H, D, V, tau):
     assert max_err(state[1], kept[3]) < tol and max_err(state[2], kept[4]) < tol and max_err(state[3], kept[0]) < tol
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("case", [c for c in ATTN_CASES if c[2] == c[3] and c[2] % 16 == 0] + [(4, 1, 128, 128, 50, 6, 25.0, True, 300)])
+def test_decode_attention_split_along_the_keys_with_the_options(dtype, splits, case):
+    from llm_b200.csrc import ops
+    H, G, D, V, window, keep, cap, sink, T = case
+    if not sink:
+        pytest.skip("covered by the general kernel's test")
+    g = torch.Generator().manual_seed(T * 3 + H)
+    page, scale = 8, 2.0 / math.sqrt(D)
+    lens = [T, 1, T // 2, window + keep + 1 if window else 5]           # four requests of unequal length decode together
+    q_rows, want, tables, kp, vp = [], [], [], [], []
+    offset = 0
+    for n in lens:
+        q, k, v = (bf(torch.randn(n, m, d, generator=g)) for m, d in ((H, D), (G, D), (G, V)))
+        want.append(P.sink_attention(q, k, v, scale, cap or 1e9, window or n + 1, keep)[-1])
+        q_rows.append(q[-1].reshape(-1))
+        k_pages, v_pages, order = _paged(k, v, page, n)
+        tables.append([o + offset for o in order])
+        offset += k_pages.shape[0]
+        kp.append(k_pages); vp.append(v_pages)
+    width = max(len(t) for t in tables) + 1
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
+    for e, t in enumerate(tables):
+        table[e, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    out = torch.empty(len(lens), H * V, device="cuda", dtype=DT[dtype])
+    ops.paged_attention_decode(out, dev(torch.stack(q_rows), dtype), dev(torch.cat(kp), dtype), dev(torch.cat(vp), dtype), table.cuda(),
+                               i32(lens), len(lens), H, G, D, window, scale, splits=splits, softcap=cap, sink=sink, keep_first=keep)
+    assert max_err(out.view(len(lens), H, V), torch.stack(want)) < (1e-5 if dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("H,D,V,tau", [(2, 16, 24, 8.0), (1, 130, 33, 1.0), (3, 64, 40, 32.0)])
+def test_gla_segments_side_by_side_equal_the_single_pass(H, D, V, tau):
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(H + D)
+    lens = [150, 1, 64, 65, 7]
+    T, cu = sum(lens), [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    x = dev(bf(torch.randn(T, 2 * H * D + H * V, generator=g) * 0.7))
+    z, b = dev(torch.randn(T, H * D, generator=g) * 2 + 2), dev(torch.randn(H * D, generator=g))
+    q, k, v = x[:, :H * D], x[:, H * D:2 * H * D], x[:, 2 * H * D:]
+    start = torch.randn(6, H, D, V, generator=g).cuda()                 # the requests come with a past
+    slots = [4, 0, 2, 5, 1]
+    s1, s2 = start.clone(), start.clone()
+    o1, o2 = torch.empty(T, H * V, device="cuda"), torch.empty(T, H * V, device="cuda")
+    ops.gla_scan(o1, q, k, v, z, b, tau, D ** -0.5, s1, i32(slots), i32(cu), len(lens))
+    for seg in (16, 64):
+        segs = T // seg + len(lens)
+        ops.gla_scan(o2, q, k, v, z, b, tau, D ** -0.5, s2, i32(slots), i32(cu), len(lens), n_tokens=T, seg_len=seg,
+                     seg_state=torch.full((segs * H * D * V,), float("nan"), device="cuda"),
+                     seg_decay=torch.full((segs * H * D,), float("nan"), device="cuda"))
+        assert max_err(o2, o1) < 1e-5 and max_err(s2, s1) < 1e-5
+        assert torch.equal(s2[3], start[3])                              # a slot that no entry names stays as it was
+        s2 = start.clone()
+
+
 @pytest.mark.parametrize("experts,top", [(1, 1), (4, 2), (7, 7), (12, 3), (37, 5)])
 def test_router_weights_are_shares_of_the_full_softmax(experts, top):
     from llm_b200.csrc import ops
