@@ -23,6 +23,12 @@
 // Visible keys of a row at position p: max(0, p-window+1) .. p.  The reference's kernel is an
 // mma.sync flash attention fixed to 32/4/64 (kernel/attention/attention_NH_32_NKV_4_HS_64.h);
 // this one takes any head counts with group size up to 128.
+//
+// The EXT instantiation adds three options.  A soft cap on the scaled scores, cap * tanh(s / cap), with the
+// hardware's tanh.approx.f32 (relative error about 2^-11, well inside what the bfloat16 rounding of q, k and P
+// does to a score).  A sink: the row's softmax starts with one term of score 0 and no value (reference 0, sum 1).
+// And, with a window, the request's first keep_first keys: the blocks that hold them are walked before the
+// window's blocks, and the mask lets them through.
 #include <mutex>
 #include <unordered_map>
 
@@ -58,6 +64,12 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -104,13 +116,15 @@ struct Smem {
   static constexpr int TOTAL = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 256 /* barriers */;
 };
 
-template <int HS>
+template <int HS, bool EXT>
 __global__ void __launch_bounds__(THREADS, HS == 64 ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long long out_stride,
                     const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_tokens,
                     const int* __restrict__ kv_lens, int n_entries, int n_heads, int n_kv, int page_size, int n_pages,
-                    int window, float scale_log2e, int* __restrict__ err_flag) {
+                    int window, float scale_log2e, int* __restrict__ err_flag, float cap_c1, float cap_c2, int sink,
+                    int keep_first) {
+  // cap_c1 = scale / cap and cap_c2 = cap * log2(e) (both 0 without a cap): a score s becomes tanh(s * c1) * c2
   using S = Smem<HS>;
   constexpr int KB = S::KB;
   constexpr uint32_t TMEM_COLS = 256;                     // S: 128 columns, O_blk: HS columns
@@ -188,7 +202,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int p_last = p0 + nt - 1;
     const int lo_tile = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;   // lowest key any row sees
     const int kb_first = lo_tile / BKV, kb_last = p_last / BKV;
-    const int n_blocks = kb_last - kb_first + 1;
+    // blocks of kept keys that lie wholly before the window's first block come first
+    const int n_keep = (EXT && window > 0 && keep_first > 0) ? min((keep_first + BKV - 1) / BKV, kb_first) : 0;
+    const int n_blocks = n_keep + kb_last - kb_first + 1;
+    auto block_of = [&](int i) { return i < n_keep ? i : kb_first + (i - n_keep); };
 
     if (warp == 0) {
       // ---- producer: the whole warp.  A block of keys (or values) is pages_per_block * KB boxes;
@@ -205,7 +222,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int i = 0; i < n_blocks && ok; ++i) {
         const int s = i % KV_STAGES;
         const uint32_t free_parity = ((i / KV_STAGES) & 1) ^ 1;
-        const int key0 = (kb_first + i) * BKV;
+        const int key0 = block_of(i) * BKV;
         for (int which = 0; which < 2 && ok; ++which) {           // keys first: the next scores need them early
           uint64_t* full = which ? &v_full[s] : &k_full[s];
           if (lane == 0) {
@@ -289,11 +306,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int pos = p0 + tok;
       const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-      float m_ref = -INFINITY, l = 0.f;
+      // with a sink the row starts with one term of score 0: reference 0, sum 1
+      float m_ref = (EXT && sink) ? 0.f : -INFINITY, l = (EXT && sink) ? 1.f : 0.f;
+      const int keep = EXT ? keep_first : 0;
+      const bool capped = EXT && cap_c2 > 0.f;
       bool ok = true;
 
       for (int i = 0; i < n_blocks; ++i) {
-        const int key0 = (kb_first + i) * BKV;
+        const int key0 = block_of(i) * BKV;
         if (ok) ok = mbar_wait(s_full, i & 1);
         fence_after_sync();
         uint32_t raw[2][64];
@@ -303,7 +323,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         fence_before_sync();
         mbar_arrive(s_free);
         // every row sees every key of the block when the block lies inside all windows and below all diagonals
-        const bool full = (key0 + BKV - 1 <= p0) && (window <= 0 || key0 >= p_last - window + 1);
+        const bool full = (key0 + BKV - 1 <= p0) &&
+                          (window <= 0 || key0 >= p_last - window + 1 || (EXT && key0 + BKV - 1 < keep));
         // the row's maximum over the block.  The scale is positive, so it is taken over the raw
         // scores and scaled once.  Four running maxima (and sums below) keep the dependent chains short.
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -317,11 +338,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 64; ++j) {
               const int key = key0 + c * 64 + j;
-              if (key <= pos && key >= lo) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[c][j]));
+              if (key <= pos && (key >= lo || key < keep)) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(raw[c][j]));
             }
           }
         }
-        const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+        const float mx_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        // the cap is monotonic, so the block's maximum is capped once (a row that sees none of the block keeps -inf)
+        const float m_blk = (capped && mx_raw != -INFINITY) ? fast_tanh(mx_raw * cap_c1) * cap_c2 : mx_raw * scale_log2e;
         // move the reference only when the block's maximum is far above it (or it is the first
         // key this row sees: -inf + TAU is -inf)
         const bool moved = m_blk > m_ref + TAU;
@@ -357,12 +380,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             float xa, xb;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(raw[c][2 * j]), __uint_as_float(raw[c][2 * j + 1])), scale2, neg_m2), xa, xb);
+            if (capped) {
+              xa = fmaf(fast_tanh(__uint_as_float(raw[c][2 * j]) * cap_c1), cap_c2, neg_m);
+              xb = fmaf(fast_tanh(__uint_as_float(raw[c][2 * j + 1]) * cap_c1), cap_c2, neg_m);
+            } else {
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(raw[c][2 * j]), __uint_as_float(raw[c][2 * j + 1])), scale2, neg_m2), xa, xb);
+            }
             float pa = fast_exp2(xa), pb = fast_exp2(xb);
             if (!full) {
               const int key = key0 + c * 64 + 2 * j;
-              if (key > pos || key < lo) pa = 0.f;
-              if (key + 1 > pos || key + 1 < lo) pb = 0.f;
+              if (key > pos || (key < lo && key >= keep)) pa = 0.f;
+              if (key + 1 > pos || (key + 1 < lo && key + 1 >= keep)) pb = 0.f;
             }
             ls2[j & 3] = add_f32x2(ls2[j & 3], pack_f32x2(pa, pb));
             const __nv_bfloat162 h2 = __floats2bfloat162_rn(pa, pb);
@@ -492,12 +520,12 @@ int get_map3(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint6
 
 int* g_attn_err = nullptr;
 
-template <int HS>
+template <int HS, bool EXT>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, long long out_stride,
            const int* block_table, int table_width, const int* cu_tokens, const int* kv_lens, int n_entries,
            int max_tiles, int n_heads, int n_kv, int page_size, int n_pages, int window, float scale_log2e,
-           cudaStream_t stream) {
-  auto kern = attention_tc_kernel<HS>;
+           cudaStream_t stream, float cap_c1, float cap_c2, int sink, int keep_first) {
+  auto kern = attention_tc_kernel<HS, EXT>;
   constexpr int smem = Smem<HS>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -507,7 +535,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   }
   dim3 grid(max_tiles * n_kv);
   launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride, block_table,
-                table_width, cu_tokens, kv_lens, n_entries, n_heads, n_kv, page_size, n_pages, window, scale_log2e, g_attn_err);
+                table_width, cu_tokens, kv_lens, n_entries, n_heads, n_kv, page_size, n_pages, window, scale_log2e, g_attn_err,
+                cap_c1, cap_c2, sink, keep_first);
   LLMK_LAUNCH_CHECK("attention_tc");
 }
 
@@ -527,8 +556,11 @@ LLMK_API int llmk_attention_tc_supported(int n_heads, int n_kv, int head_dim, in
 LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, long long q_stride, const void* k_pages,
                                const void* v_pages, int n_pages, const int* block_table, int table_width,
                                const int* cu_tokens, const int* kv_lens, int n_tokens, int n_entries, int n_heads,
-                               int n_kv, int head_dim, int page_size, int window, float scale, cudaStream_t stream) {
+                               int n_kv, int head_dim, int page_size, int window, float scale, cudaStream_t stream,
+                               float softcap, int sink, int keep_first) {
   if (n_tokens == 0 || n_entries == 0) return 0;
+  LLMK_REQUIRE(softcap >= 0.f && keep_first >= 0, "attention_tc: bad soft cap %f or keep_first %d", (double)softcap, keep_first);
+  if (window == 0) keep_first = 0;
   LLMK_REQUIRE(llmk_attention_tc_supported(n_heads, n_kv, head_dim, page_size),
                "attention_tc: needs head_dim 64 or 128, page_size 16/32/64/128 and at most %d query heads per kv head "
                "(got heads %d/%d, head_dim %d, page_size %d)", ROWS, n_heads, n_kv, head_dim, page_size);
@@ -543,11 +575,14 @@ LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, l
   if ((rc = get_map3(&mk, k_pages, head_dim, page_size, (uint64_t)n_pages * n_kv, head_dim, (uint64_t)page_size * head_dim, page_size, 1))) return rc;
   if ((rc = get_map3(&mv, v_pages, head_dim, page_size, (uint64_t)n_pages * n_kv, head_dim, (uint64_t)page_size * head_dim, page_size, 1))) return rc;
   const float scale_log2e = scale * 1.4426950408889634f;
-  if (head_dim == 64)
-    return launch<64>(mq, mk, mv, out, out_stride, block_table, table_width, cu_tokens, kv_lens, n_entries, max_tiles,
-                      n_heads, n_kv, page_size, n_pages, window, scale_log2e, stream);
-  return launch<128>(mq, mk, mv, out, out_stride, block_table, table_width, cu_tokens, kv_lens, n_entries, max_tiles,
-                     n_heads, n_kv, page_size, n_pages, window, scale_log2e, stream);
+  const float c1 = softcap > 0.f ? scale / softcap : 0.f, c2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+#define LLMK_ATTN_TC(HS, EXT)                                                                                             \
+  launch<HS, EXT>(mq, mk, mv, out, out_stride, block_table, table_width, cu_tokens, kv_lens, n_entries, max_tiles, n_heads, \
+                  n_kv, page_size, n_pages, window, scale_log2e, stream, c1, c2, sink, keep_first)
+  const bool ext = softcap > 0.f || sink || keep_first > 0;
+  if (head_dim == 64) return ext ? LLMK_ATTN_TC(64, true) : LLMK_ATTN_TC(64, false);
+  return ext ? LLMK_ATTN_TC(128, true) : LLMK_ATTN_TC(128, false);
+#undef LLMK_ATTN_TC
 }
 
 // The code the attention kernel left when one of its bounded waits gave up (0 = none).

@@ -658,9 +658,11 @@ def attention_tc_supported(dtype, n_heads: int, n_kv: int, head_dim: int, page_s
 
 def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                  block_table: torch.Tensor, cu_tokens: torch.Tensor, kv_lens: torch.Tensor, n_tokens: int,
-                 n_entries: int, n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
+                 n_entries: int, n_heads: int, n_kv: int, head_dim: int, window: int, scale: float,
+                 softcap: float = 0.0, sink: bool = False, keep_first: int = 0) -> None:
     """Flash attention on the tensor cores for entries of any length: rows of entry e are
-    cu_tokens[e] .. cu_tokens[e+1], its keys (new tokens included) number kv_lens[e]."""
+    cu_tokens[e] .. cu_tokens[e+1], its keys (new tokens included) number kv_lens[e].
+    softcap, sink, keep_first: as in paged_attention_generic."""
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
@@ -670,7 +672,8 @@ def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pa
         _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
         c_int(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]), _ptr(cu_tokens), _ptr(kv_lens),
         c_int(n_tokens), c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(k_pages.shape[2]),
-        c_int(window or 0), c_float(scale), _stream()))
+        c_int(window or 0), c_float(scale), _stream(), c_float(softcap or 0.0), c_int(int(bool(sink))),
+        c_int(keep_first or 0)))
 
 
 def attention_tc_take_error() -> int:
@@ -698,6 +701,11 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
                                n_heads, n_kv, head_dim, window, scale,
                                splits=decode_splits(ctx.n_entries, n_kv, max_keys), max_keys=max_keys,
                                softcap=softcap, sink=sink, keep_first=keep_first)
+        return
+    if (extended and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
+            and attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2])):
+        attention_tc(out, qkv, k_pages, v_pages, group.block_table, ctx.cu_tokens, ctx.kv_lens, ctx.n_tokens,
+                     ctx.n_entries, n_heads, n_kv, head_dim, window, scale, softcap=softcap, sink=sink, keep_first=keep_first)
         return
     if extended:
         paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,

@@ -282,6 +282,44 @@ def test_decode_attention_split_along_the_keys_with_the_options(dtype, splits, c
     assert max_err(out.view(len(lens), H, V), torch.stack(want)) < (1e-5 if dtype == "float32" else 8e-3)
 
 
+TC_CASES = [  # H, G, D, window, keep_first, softcap, sink, prompt length, tokens already in the cache
+    (8, 2, 64, 200, 150, 20.0, True, 600, 0),
+    (4, 1, 128, 70, 4, 30.0, True, 300, 217),
+    (16, 4, 64, 129, 0, 0.0, True, 400, 0),
+    (2, 2, 128, 0, 0, 15.0, False, 260, 5),
+    (8, 8, 64, 300, 257, 10.0, True, 700, 0),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_prompt_attention_on_the_tensor_cores_with_the_options(case):
+    from llm_b200.csrc import ops
+    H, G, D, window, keep, cap, sink, T, past = case
+    g = torch.Generator().manual_seed(T + H)
+    page, scale, n = 16, 1.5 / math.sqrt(D), T + past
+    q, k, v = (bf(torch.randn(n, m, D, generator=g)) for m in (H, G, G))
+    want = P.sink_attention(q, k, v, scale, cap or 1e9, window or n + 1, keep)[past:]
+    if not sink:                                         # the plain side always has the sink: take its share out again
+        for i in range(past, n):
+            js = [j for j in range(i + 1) if P.visible(i, j, window or n + 1, keep)]
+            for h in range(H):
+                sc = (k[js, h // (H // G)].double() @ q[i, h].double()) * scale
+                e = torch.exp((cap or 1e9) * torch.tanh(sc / (cap or 1e9))).sum()
+                want[i - past, h] *= (1.0 + e) / e
+    k_pages, v_pages, order = _paged(k, v, page, T)
+    table = torch.full((3, len(order) + 1), -1, dtype=torch.int32)
+    table[1, :len(order)] = torch.tensor(order, dtype=torch.int32)
+    # the entry in the middle of a batch of three; its neighbours bring a token each over pages of their own
+    kp, vp = dev(k_pages, "bfloat16"), dev(v_pages, "bfloat16")
+    table[0, 0] = table[2, 0] = order[0]
+    rows = torch.cat([q[:1], q[past:], q[:1]]).view(T + 2, H * D)
+    out = torch.empty(T + 2, H * D, device="cuda", dtype=torch.bfloat16)
+    ops.attention_tc(out, dev(rows, "bfloat16"), kp, vp, table.cuda(), i32([0, 1, T + 1, T + 2]), i32([1, n, 1]), T + 2, 3, H, G, D,
+                     window, scale, softcap=cap, sink=sink, keep_first=keep)
+    assert ops.attention_tc_take_error() == 0
+    assert max_err(out[1:T + 1].view(T, H, D), want) < 1e-2
+
+
 @pytest.mark.parametrize("H,D,V,tau", [(2, 16, 24, 8.0), (1, 130, 33, 1.0), (3, 64, 40, 32.0)])
 def test_gla_segments_side_by_side_equal_the_single_pass(H, D, V, tau):
     from llm_b200.csrc import ops
