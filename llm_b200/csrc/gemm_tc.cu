@@ -1165,6 +1165,9 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
 // mode 2 (by_tile): A [M, K] with M a multiple of 128 (rows sorted by group, runs padded to whole tiles),
 //   W [groups * N, K], C [M, ldc]; tile_group [M / 128] and n_tiles [1] on the device.  persistent != 0: more tiles
 //   than SMs run on the persistent kernel (one CTA per SM, two accumulators).
+//   act 4 (by_tile only): gated experts.  A group's N rows of W are N/2 gate rows followed by N/2 up rows, and C
+//   [M, N/2] bfloat16 receives silu(gate) * up from the persistent kernel's epilogue (a tile multiplies by 128 gate rows
+//   and their 128 up rows), so the stacked product never reaches memory.
 LLMK_API int llmk_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
                                   long long ldc, int out_dtype, int mode, int groups, int a_k_step, long long c_step,
                                   const int* tile_group, const int* n_tiles, int act, const void* gate,
@@ -1174,9 +1177,17 @@ LLMK_API int llmk_gemm_tc_grouped(const void* A, const void* W, void* C, int M, 
   LLMK_REQUIRE(llmk_gemm_tc_supported(A, W, M, N, K, lda, ldw), "gemm_tc_grouped: K=%d and the row pitches must be multiples of 8 and the bases 16-byte aligned", K);
   LLMK_REQUIRE(mode != 1 || (a_k_step % 8 == 0 && K <= a_k_step && groups <= 65535), "gemm_tc_grouped: a_k_step %d must be a multiple of 8 and at least K=%d", a_k_step, K);
   LLMK_REQUIRE(mode != 2 || (M % BP == 0 && tile_group && n_tiles), "gemm_tc_grouped: by_tile needs M=%d a multiple of %d and the tile table", M, BP);
-  LLMK_REQUIRE(act >= -1 && act <= 3, "gemm_tc_grouped: unknown activation %d", act);
+  LLMK_REQUIRE(act >= -1 && act <= 4, "gemm_tc_grouped: unknown activation %d", act);
   int rc = ensure_err_flag();
   if (rc) return rc;
+  if (act == 4) {
+    LLMK_REQUIRE(mode == 2 && out_dtype == LLMK_BF16 && N % 2 == 0, "gemm_tc_grouped: gated experts run by row tile into bfloat16 (N=%d even)", N);
+    CUtensorMap ma, mw;
+    if ((rc = get_map(&ma, A, M, (uint64_t)K, lda, BP))) return rc;
+    if ((rc = get_map(&mw, W, (uint64_t)groups * N, K, ldw, 128))) return rc;
+    const Grouping gated{mode, a_k_step, N, tile_group, n_tiles, -1, nullptr, 0};
+    return launch_persistent<__nv_bfloat16, true>(ma, mw, C, ldc, M, N, K, 256, stream, gated);
+  }
   // the tile of weight rows: as wide as the product where that is at most 256 (in steps of 32), else 256 or 128
   int tile = (N + 31) / 32 * 32;
   if (tile > 256) tile = (N % 256 == 0 || N % 256 > 128) ? 256 : 128;

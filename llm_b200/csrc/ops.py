@@ -250,7 +250,7 @@ def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     pre-activation (+ z_bias), state float32 [slots, heads, dim, vdim] read and written at state_slots[entry],
     out float32 [T, heads*vdim].  seg_len > 0: entries run as segments of that many tokens side by side, in two passes;
     n_tokens is the step's token count and seg_state / seg_decay are float32 scratch for n_tokens // seg_len + n_entries
-    segments ([.., heads, dim, vdim] and [.., heads, dim])."""
+    segments ([.., heads, dim, vdim] and [.., heads, dim]); z is then overwritten with the decays."""
     heads, dim, vdim = state.shape[1], state.shape[2], state.shape[3]
     if seg_len:
         segs = n_tokens // seg_len + n_entries
@@ -268,7 +268,7 @@ def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
                                 _ptr(cu_tokens), c_int(n_entries), c_int(heads), c_int(dim), c_int(vdim), c_int(_kind(q.dtype)),
                                 _stream(), c_int(n_tokens), c_int(seg_len), _ptr(seg_state), _ptr(seg_decay)))
     if seg_len:
-        count_launches(2)
+        count_launches(3)
 
 
 ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
@@ -392,15 +392,18 @@ def moe_gemm_tc_available(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 def moe_gemm_tc(a: torch.Tensor, tile_expert, meta, w: torch.Tensor, out: torch.Tensor, max_tiles: int, act=None) -> None:
     """out[slot] = act(a[slot] @ w[expert of the slot's tile].T) on the tensor cores: a [slots, K] in slot order
-    (tiles of 128 slots), w [experts, N, K], out bfloat16 or float32 [slots, N]."""
+    (tiles of 128 slots), w [experts, N, K], out bfloat16 or float32 [slots, N].  act "silu_gate": an expert's N rows
+    are N/2 gate rows followed by N/2 up rows and out [slots, N/2] bfloat16 = silu(gate) * up, made in the epilogue."""
     _rows_contig(a, "a"); _rows_contig(out, "out")
-    assert w.dim() == 3 and w.is_contiguous() and a.shape[1] == w.shape[2] and out.shape[1] == w.shape[1]
+    gated = act == "silu_gate"
+    assert w.dim() == 3 and w.is_contiguous() and a.shape[1] == w.shape[2] and out.shape[1] == (w.shape[1] // 2 if gated else w.shape[1])
+    assert not gated or (out.dtype == torch.bfloat16 and w.shape[1] % 2 == 0)
     rows = max_tiles * MOE_TC_TILE
     assert a.shape[0] >= rows and out.shape[0] >= rows
     _check_t(load_tensor().llmk_gemm_tc_grouped(
         _ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(w.shape[1]), c_int(w.shape[2]), c_longlong(a.stride(0)),
         c_longlong(w.shape[2]), c_longlong(out.stride(0)), c_int(_kind(out.dtype)), c_int(2), c_int(w.shape[0]), c_int(0),
-        c_longlong(0), _ptr(tile_expert), _ptr(meta), c_int(ACTIVATIONS[act] if act else -1), c_void_p(0), c_longlong(0),
+        c_longlong(0), _ptr(tile_expert), _ptr(meta), c_int(4 if gated else ACTIVATIONS[act] if act else -1), c_void_p(0), c_longlong(0),
         c_int(int(GROUPED_PERSISTENT)), _stream()))
 
 

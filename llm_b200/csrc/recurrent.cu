@@ -10,11 +10,12 @@
 // Everything that enters the recurrence is float32: decay, its logarithm, state, sums; q, k, v
 // are read in the element kind of the projections.
 //
-// Work split: a CTA owns one (entry, head, tile of VT value columns); thread (j, g) keeps the 16
-// state rows d = 16 g .. 16 g + 15 of column j in registers.  Tokens are staged in shared memory
-// CHUNK at a time (q, k, a once per CTA, broadcast to the threads of a row group); each thread
-// updates its rows and keeps a partial o per token, and the partial sums of the row groups are
-// added in the order of g after every chunk.
+// Work split: a CTA owns one (entry, head, tile of VT value columns); thread (j, g) keeps the 8 x 4
+// block of the state at rows d = 8 g .. 8 g + 7, columns 4 j .. 4 j + 3 in registers, so that every
+// value of q, k, a and v it loads from shared memory serves four or eight multiply-adds.  Tokens are
+// staged in shared memory CHUNK at a time (q, k, a once per CTA); each thread updates its block and
+// keeps partial outputs per token, and the partial sums of the row groups are added in the order of g
+// after every chunk.
 //
 // Long entries (prompts) are cut into segments of seg_len tokens that run side by side, since one
 // entry alone offers only heads x vdim x dim / 16 threads: pass 1 walks every segment from a zero
@@ -28,25 +29,28 @@
 
 namespace {
 
-constexpr int ROWS = 16;      // state rows per thread
+constexpr int ROWS = 8;       // state rows per thread
+constexpr int COLS = 4;       // state columns per thread
 constexpr int CHUNK = 8;      // tokens staged at a time
-constexpr int MAX_GROUPS = 16;
+constexpr int MAX_GROUPS = 32;
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 template <typename T, int VT>
-__global__ void __launch_bounds__(VT * MAX_GROUPS)
+__global__ void __launch_bounds__(VT / COLS * MAX_GROUPS)
 gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restrict__ q, const T* __restrict__ k,
                 const T* __restrict__ v, long long qkv_stride, const float* __restrict__ z, long long z_stride,
                 const float* __restrict__ z_bias, float inv_tau, float q_scale, float* __restrict__ state,
                 const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, int heads, int dim, int vdim,
-                int seg_len, int max_segs, int mode, float* __restrict__ seg_state, float* __restrict__ seg_decay) {
-  extern __shared__ float smem[];
+                int seg_len, int max_segs, int mode, float* __restrict__ seg_state, float* __restrict__ seg_decay,
+                int z_is_decay) {
+  extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   // mode 0: the whole entry from its request's state, which is written back.  mode 1 (pass 1 of a segmented run):
   // a segment from zero, no outputs; its end state and decay product go to seg_state / seg_decay.  mode 2 (pass 2):
   // a segment from seg_state (by then its true start), outputs only.
+  constexpr int TX = VT / COLS;               // threads along the columns
   const int groups = blockDim.y, dpad = groups * ROWS;
   float* q_s = smem;                          // [CHUNK][dpad]
   float* k_s = q_s + CHUNK * dpad;
@@ -54,8 +58,9 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
   float* v_s = a_s + CHUNK * dpad;            // [CHUNK][VT]
   float* part = v_s + CHUNK * VT;             // [CHUNK][groups][VT]
   const int j = threadIdx.x, g = threadIdx.y;
-  const int tid = g * VT + j, nthreads = VT * groups;
-  const int entry = blockIdx.z / max_segs, seg = blockIdx.z % max_segs, head = blockIdx.y, col = blockIdx.x * VT + j;
+  const int tid = g * TX + j, nthreads = TX * groups;
+  const int entry = blockIdx.z / max_segs, seg = blockIdx.z % max_segs, head = blockIdx.y;
+  const int col0 = blockIdx.x * VT + j * COLS;
   int t0 = cu_tokens[entry], t1 = cu_tokens[entry + 1];
   size_t seg_index = 0;
   if (mode != 0) {
@@ -67,29 +72,32 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
   }
   float* S_g = mode == 0 ? state + (((size_t)state_slots[entry] * heads + head) * dim) * vdim
                          : seg_state + ((seg_index * heads + head) * dim) * vdim;
-  const bool col_ok = col < vdim;
 
-  float S[ROWS], A[ROWS];
+  float S[ROWS][COLS], A[ROWS];
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) {
-    const int d = g * ROWS + i;
-    S[i] = (mode != 1 && col_ok && d < dim) ? S_g[(size_t)d * vdim + col] : 0.f;
-    A[i] = 1.f;
+  for (int r = 0; r < ROWS; ++r) {
+    const int d = g * ROWS + r;
+#pragma unroll
+    for (int c = 0; c < COLS; ++c)
+      S[r][c] = (mode != 1 && d < dim && col0 + c < vdim) ? S_g[(size_t)d * vdim + col0 + c] : 0.f;
+    A[r] = 1.f;
   }
   for (int c0 = t0; c0 < t1; c0 += CHUNK) {
     const int n = min(CHUNK, t1 - c0);
     __syncthreads();                          // the previous chunk's partial sums have been read
-    for (int idx = tid; idx < n * dpad; idx += nthreads) {
-      const int c = idx / dpad, d = idx % dpad;
-      float qv = 0.f, kv = 0.f, av = 0.f;
-      if (d < dim) {
-        const size_t at = (size_t)(c0 + c) * qkv_stride + (size_t)head * dim + d;
-        qv = to_f32(q[at]) * q_scale;
-        kv = to_f32(k[at]);
-        const float zz = z[(size_t)(c0 + c) * z_stride + (size_t)head * dim + d] + (z_bias ? z_bias[head * dim + d] : 0.f);
-        av = expf(log_sigmoid(zz) * inv_tau);
+    for (int c = 0; c < n; ++c) {
+      for (int d = tid; d < dpad; d += nthreads) {
+        float qv = 0.f, kv = 0.f, av = 0.f;
+        if (d < dim) {
+          const size_t at = (size_t)(c0 + c) * qkv_stride + (size_t)head * dim + d;
+          if (mode != 1) qv = to_f32(q[at]) * q_scale;
+          kv = to_f32(k[at]);
+          const float zz = z[(size_t)(c0 + c) * z_stride + (size_t)head * dim + d];
+          // the two passes of a segmented run read the decay itself, made once by gla_decay_kernel
+          av = z_is_decay ? zz : expf(log_sigmoid(zz + (z_bias ? z_bias[head * dim + d] : 0.f)) * inv_tau);
+        }
+        q_s[c * dpad + d] = qv; k_s[c * dpad + d] = kv; a_s[c * dpad + d] = av;
       }
-      q_s[idx] = qv; k_s[idx] = kv; a_s[idx] = av;
     }
     for (int idx = tid; idx < n * VT; idx += nthreads) {
       const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
@@ -97,25 +105,40 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
     }
     __syncthreads();
     for (int c = 0; c < n; ++c) {
-      const float vv = v_s[c * VT + j];
-      const float* qc = q_s + c * dpad + g * ROWS;
-      const float* kc = k_s + c * dpad + g * ROWS;
-      const float* ac = a_s + c * dpad + g * ROWS;
-      float o = 0.f;
+      // the thread's 8 rows of k, a (and q) and its 4 values of v: 16-byte loads, shared by the threads of a row group
+      const float4 v4 = *reinterpret_cast<const float4*>(v_s + c * VT + j * COLS);
+      const float vv[COLS] = {v4.x, v4.y, v4.z, v4.w};
+      float kc[ROWS], ac[ROWS], qc[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; r += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(k_s + c * dpad + g * ROWS + r);
+        const float4 a4 = *reinterpret_cast<const float4*>(a_s + c * dpad + g * ROWS + r);
+        kc[r] = k4.x; kc[r + 1] = k4.y; kc[r + 2] = k4.z; kc[r + 3] = k4.w;
+        ac[r] = a4.x; ac[r + 1] = a4.y; ac[r + 2] = a4.z; ac[r + 3] = a4.w;
+        if (mode != 1) {
+          const float4 q4 = *reinterpret_cast<const float4*>(q_s + c * dpad + g * ROWS + r);
+          qc[r] = q4.x; qc[r + 1] = q4.y; qc[r + 2] = q4.z; qc[r + 3] = q4.w;
+        }
+      }
       if (mode == 1) {
 #pragma unroll
-        for (int i = 0; i < ROWS; ++i) {
-          S[i] = fmaf(ac[i], S[i], kc[i] * vv);
-          A[i] *= ac[i];
+        for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+          for (int cc = 0; cc < COLS; ++cc) S[r][cc] = fmaf(ac[r], S[r][cc], kc[r] * vv[cc]);
+          A[r] *= ac[r];
         }
         continue;
       }
+      float o[COLS] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < ROWS; ++i) {
-        S[i] = fmaf(ac[i], S[i], kc[i] * vv);
-        o = fmaf(S[i], qc[i], o);
+      for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+        for (int cc = 0; cc < COLS; ++cc) {
+          S[r][cc] = fmaf(ac[r], S[r][cc], kc[r] * vv[cc]);
+          o[cc] = fmaf(S[r][cc], qc[r], o[cc]);
+        }
       }
-      part[(c * groups + g) * VT + j] = o;
+      *reinterpret_cast<float4*>(part + (c * groups + g) * VT + j * COLS) = make_float4(o[0], o[1], o[2], o[3]);
     }
     if (mode == 1) continue;
     __syncthreads();
@@ -129,10 +152,26 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
   }
   if (mode == 2) return;
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) {
-    const int d = g * ROWS + i;
-    if (col_ok && d < dim) S_g[(size_t)d * vdim + col] = S[i];
-    if (mode == 1 && blockIdx.x == 0 && j == 0 && d < dim) seg_decay[(seg_index * heads + head) * dim + d] = A[i];
+  for (int r = 0; r < ROWS; ++r) {
+    const int d = g * ROWS + r;
+    if (d >= dim) continue;
+#pragma unroll
+    for (int c = 0; c < COLS; ++c)
+      if (col0 + c < vdim) S_g[(size_t)d * vdim + col0 + c] = S[r][c];
+    if (mode == 1 && blockIdx.x == 0 && j == 0) seg_decay[(seg_index * heads + head) * dim + d] = A[r];
+  }
+}
+
+// z <- sigmoid(z + bias)^(1 / tau) in place: the decays of a step, made once where several CTAs and two passes read them.
+__global__ void gla_decay_kernel(float* __restrict__ z, long long z_stride, const float* __restrict__ z_bias, float inv_tau,
+                                 int cols, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / cols;
+    const int c = (int)(i - t * cols);
+    float* at = z + t * z_stride + c;
+    *at = expf(log_sigmoid(*at + (z_bias ? z_bias[c] : 0.f)) * inv_tau);
   }
 }
 
@@ -172,9 +211,9 @@ __global__ void gla_chain_kernel(float* __restrict__ seg_state, const float* __r
 // a column do not depend on the tile's width.
 // seg_len > 0: entries run as segments of seg_len tokens in two passes (see the head of the file); n_tokens is then the
 // step's number of tokens, seg_state float32 [n_tokens / seg_len + n_entries, heads, dim, vdim] and seg_decay
-// [same, heads, dim] scratch.  seg_len 0: one pass.
+// [same, heads, dim] scratch, and z is overwritten with the decays.  seg_len 0: one pass.
 LLMK_API int llmk_gla_scan(float* out, long long out_stride, const void* q, const void* k, const void* v,
-                           long long qkv_stride, const float* z, long long z_stride, const float* z_bias, float tau,
+                           long long qkv_stride, float* z, long long z_stride, const float* z_bias, float tau,
                            float q_scale, float* state, const int* state_slots, const int* cu_tokens, int n_entries,
                            int heads, int dim, int vdim, int dtype, cudaStream_t stream, int n_tokens, int seg_len,
                            float* seg_state, float* seg_decay) {
@@ -195,9 +234,11 @@ LLMK_API int llmk_gla_scan(float* out, long long out_stride, const void* q, cons
     using T = LLMK_ELEM(tag);
     auto launch = [&](auto kern, int VT, int mode) {
       const size_t smem = sizeof(float) * ((size_t)CHUNK * groups * ROWS * 3 + (size_t)CHUNK * VT + (size_t)CHUNK * groups * VT);
-      return launch_kernel(kern, dim3((vdim + VT - 1) / VT, heads, n_entries * max_segs), dim3(VT, groups), smem, stream, out,
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      return launch_kernel(kern, dim3((vdim + VT - 1) / VT, heads, n_entries * max_segs), dim3(VT / COLS, groups), smem, stream, out,
                            out_stride, (const T*)q, (const T*)k, (const T*)v, qkv_stride, z, z_stride, z_bias, 1.f / tau, q_scale,
-                           state, state_slots, cu_tokens, heads, dim, vdim, seg_len, max_segs, mode, seg_state, seg_decay);
+                           state, state_slots, cu_tokens, heads, dim, vdim, seg_len, max_segs, mode, seg_state, seg_decay,
+                           seg_len ? 1 : 0);
     };
     auto pass = [&](int mode) {
       if (vt == 32) launch(gla_scan_kernel<T, 32>, 32, mode);
@@ -207,6 +248,10 @@ LLMK_API int llmk_gla_scan(float* out, long long out_stride, const void* q, cons
     if (seg_len == 0) {
       pass(0);
     } else {
+      const size_t total = (size_t)n_tokens * heads * dim;
+      size_t blocks = (total + 255) / 256;
+      if (blocks > (size_t)sms * 8) blocks = (size_t)sms * 8;
+      launch_kernel(gla_decay_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, z, z_stride, z_bias, 1.f / tau, heads * dim, total);
       pass(1);
       const size_t per = (size_t)heads * dim * vdim;
       launch_kernel(gla_chain_kernel, dim3((unsigned)((per + 255) / 256), n_entries), dim3(256), 0, stream, seg_state,

@@ -25,6 +25,10 @@ from .base import ParamInfo, Part, register_part
 from .feed_forward import ActMLP
 
 
+import os
+FUSE_GATE = os.environ.get("LLM_B200_FUSE_GATE", "1") != "0"
+
+
 class RoutedFFN(Part):
     role = "ffn"
 
@@ -90,18 +94,23 @@ class RoutedFFN(Part):
         logits = ws.get("moe_logits", T, E, f32)
         ops.moe_route(x, self.w_router, self.b_router, logits, ids, wts, T, top, over_all=self.over_all)
         ops.moe_group(ids, pairs, E, meta, tile_expert, slot_src, pair_slot, max_tiles, tile)
-        # gated experts: the up product leaves [gate, up] per slot and a row kernel makes silu(gate) * up of it
-        up_out = (ws.flat("moe_gate_up", cap_slots * 2 * self.expert_size, self.dtype).view(cap_slots, 2 * self.expert_size)
-                  if self.gated else act)
-        up_act = None if self.gated else self.activation
         if tensor:
+            # gated experts: a tile multiplies by its expert's gate rows and up rows and the epilogue makes silu(gate) * up
             rows = ws.flat("moe_rows", cap_slots * self.hidden_size, self.dtype).view(cap_slots, self.hidden_size)
             ops.moe_gather(rows, x, slot_src, meta, top, tile, max_tiles)
-            ops.moe_gemm_tc(rows, tile_expert, meta, self.w_up, up_out, max_tiles, act=up_act)
-        else:
-            ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, up_out, max_tiles, act=up_act)
-        if self.gated:
+            if self.gated and not FUSE_GATE:
+                up_out = ws.flat("moe_gate_up", cap_slots * 2 * self.expert_size, self.dtype).view(cap_slots, 2 * self.expert_size)
+                ops.moe_gemm_tc(rows, tile_expert, meta, self.w_up, up_out, max_tiles)
+                ops.silu_mul(act[:max_tiles * tile], up_out[:max_tiles * tile], max_tiles * tile)
+            else:
+                ops.moe_gemm_tc(rows, tile_expert, meta, self.w_up, act, max_tiles, act="silu_gate" if self.gated else self.activation)
+        elif self.gated:
+            # on the CUDA cores the up product leaves [gate, up] per slot and a row kernel makes silu(gate) * up of it
+            up_out = ws.flat("moe_gate_up", cap_slots * 2 * self.expert_size, self.dtype).view(cap_slots, 2 * self.expert_size)
+            ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, up_out, max_tiles)
             ops.silu_mul(act[:max_tiles * tile], up_out[:max_tiles * tile], max_tiles * tile)
+        else:
+            ops.moe_gemm(x, top, slot_src, tile_expert, meta, self.w_up, act, max_tiles, act=self.activation)
         if tensor:
             ops.moe_gemm_tc(act, tile_expert, meta, self.w_down, y, max_tiles)
         else:

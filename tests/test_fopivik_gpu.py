@@ -338,7 +338,7 @@ def test_gla_segments_side_by_side_equal_the_single_pass(H, D, V, tau):
     ops.gla_scan(o1, q, k, v, z, b, tau, D ** -0.5, s1, i32(slots), i32(cu), len(lens))
     for seg in (16, 64):
         segs = T // seg + len(lens)
-        ops.gla_scan(o2, q, k, v, z, b, tau, D ** -0.5, s2, i32(slots), i32(cu), len(lens), n_tokens=T, seg_len=seg,
+        ops.gla_scan(o2, q, k, v, z.clone(), b, tau, D ** -0.5, s2, i32(slots), i32(cu), len(lens), n_tokens=T, seg_len=seg,   # z is overwritten
                      seg_state=torch.full((segs * H * D * V,), float("nan"), device="cuda"),
                      seg_decay=torch.full((segs * H * D,), float("nan"), device="cuda"))
         assert max_err(o2, o1) < 1e-5 and max_err(s2, s1) < 1e-5
@@ -428,7 +428,8 @@ def models():
     return get
 
 
-def compare(got, ref, dtype, what):
+def compare(got, ref, dtype, what, tol=None):
+    tol = tol or TOL[dtype]
     for rid, r in ref.items():
         assert got[rid].shape == r.shape, f"{what}: {rid} shape {got[rid].shape} vs {r.shape}"
         err_rows = (got[rid].double() - r).abs().max(dim=1).values / r.abs().max()
@@ -436,9 +437,9 @@ def compare(got, ref, dtype, what):
         if margin is not None:
             unclear = margin < CLOSE_CALL[dtype]
             err_rows = torch.where(unclear, torch.zeros_like(err_rows), err_rows)
-        bad = torch.nonzero(err_rows > TOL[dtype])
+        bad = torch.nonzero(err_rows > tol)
         assert bad.numel() == 0, (f"{what}: request {rid} first differs at position {int(bad[0])} "
-                                  f"(err {float(err_rows[int(bad[0])]):.3e}, limit {TOL[dtype]:.1e})")
+                                  f"(err {float(err_rows[int(bad[0])]):.3e}, limit {tol:.1e})")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -669,7 +670,10 @@ def test_seeded_random_configurations(seed, dtype):
     reqs = {f"r{i}": random_tokens(n, cfg["vocab"], 40 + i) for i, n in enumerate([3, 45, 70, 131])}
     ref = {rid: plain_with_margin(cfg, w, toks) for rid, toks in reqs.items()}
     eng = make_engine(cfg, w, dtype[:8], page, sum(-(-len(t) // page) for t in reqs.values()) + 1)
-    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, f"seed {seed} whole")
-    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs, tail=20)), ref, dtype, f"seed {seed} tail decode")
-    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, f"seed {seed} mixed")
+    # the drawn constants include the harshest for bfloat16 (a residual multiplier of 1 under a logit cap of 10): its bound is
+    # wider here than for the models above; float32, where every row is held to 3e-5, says whether the arithmetic is right
+    tol = TOL[dtype] * (1.0 if dtype == "float32" else 1.6)
+    compare(replay.run_steps(eng, replay.steps_whole(reqs)), ref, dtype, f"seed {seed} whole", tol)
+    compare(replay.run_steps(eng, replay.steps_tail_decode(reqs, tail=20)), ref, dtype, f"seed {seed} tail decode", tol)
+    compare(replay.run_steps(eng, replay.steps_mixed(reqs)), ref, dtype, f"seed {seed} mixed", tol)
     eng.cache.check()
