@@ -438,11 +438,21 @@ def design_comparison(args, peaks, design: str = "tevudra") -> int:
     rng = np.random.default_rng(3)
     prompt_len, ctx_len, tokens = 2048, 512, args.prompt_tokens
 
-    def kernels_of(run):
+    def kernels_of(run, eng):
+        # with programmatic dependent launch a kernel starts while its predecessor still runs and waits for it, and
+        # the profiler would count that wait as the kernel's own time: the per-kernel times are taken without it,
+        # kernel by kernel (a captured graph would carry the dependent launches it was captured with)
+        from llm_b200.csrc import ops as _ops
         torch.cuda.synchronize()
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            run()
-            torch.cuda.synchronize()
+        graphs, eng.options.use_cuda_graphs = eng.options.use_cuda_graphs, False
+        _ops.set_pdl(False)
+        try:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                run()
+                torch.cuda.synchronize()
+        finally:
+            _ops.set_pdl(True)
+            eng.options.use_cuda_graphs = graphs
         agg = collections.OrderedDict()
         for e in prof.events():
             if e.device_type != torch.autograd.DeviceType.CUDA or not e.name or "Memcpy" in e.name or "Memset" in e.name:
@@ -475,7 +485,7 @@ def design_comparison(args, peaks, design: str = "tevudra") -> int:
             reps.append(a.elapsed_time(b))
         ms = sorted(reps)[len(reps) // 2]
         out["prefill"] = {"tokens": tokens, "ms": round(ms, 3), "tok_s": round(tokens / ms * 1e3)}
-        out["prefill_kernels"] = kernels_of(lambda: one_prompt(99))
+        out["prefill_kernels"] = kernels_of(lambda: one_prompt(99), eng)
         out["decode"] = {}
         for batch in (8, 64):
             ids = [f"d{batch}_{i}" for i in range(batch)]
@@ -496,7 +506,7 @@ def design_comparison(args, peaks, design: str = "tevudra") -> int:
             ms = a.elapsed_time(b) / steps
             out["decode"][str(batch)] = {"ms_per_step": round(ms, 4), "tok_s": round(batch / ms * 1e3), "context": ctx_len + warm + steps}
             if batch == 8:
-                out["decode_kernels"] = kernels_of(lambda: eng.step(entries(warm + steps)))
+                out["decode_kernels"] = kernels_of(lambda: eng.step(entries(warm + steps)), eng)
             for r in ids:
                 eng.release(r)
         del llm, eng

@@ -48,7 +48,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     pool_tokens = (args.max_tokens + 63) // 64 * 64
     # no request can hold more than the pool does; a model without a length limit of its own is sized by that
     max_pos = min(getattr(cfg, "max_position_embeddings"), pool_tokens)
-    per_step = min(max(pool_tokens, 64), 8192)
+    per_step = min(max(pool_tokens, 64), 32768)
     options = EngineOptions(
         dtype=args.dtype, kv_block_size=page, max_num_seqs=args.max_live,
         max_num_batched_tokens=per_step, max_logit_rows=per_step, max_seq_len=max_pos,

@@ -368,10 +368,13 @@ class _Ctx:
         self.n_tokens, self.workspace = rows, Workspace(max_rows, torch.device("cuda"))
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("experts,top,ff,rows", [(4, 2, 24, 50), (3, 3, 16, 7), (5, 1, 12, 33), (6, 2, 64, 300), (1, 1, 8, 3)])
-def test_gated_experts_under_the_full_softmax_router(dtype, experts, top, ff, rows):
+@pytest.mark.parametrize("experts,top,ff,rows", [(4, 2, 24, 50), (3, 3, 16, 7), (5, 1, 12, 33), (6, 2, 64, 300), (1, 1, 8, 3), (3, 2, 200, 70)])
+def test_gated_experts_under_the_full_softmax_router(dtype, experts, top, ff, rows, fused, monkeypatch):
+    from llm_b200.parts import routed
     from llm_b200.parts.routed import RoutedFFN
+    monkeypatch.setattr(routed, "FUSE_GATE_FROM_WIDTH", 0 if fused else 1 << 30)      # the activation in the product's epilogue, or after it
     g = torch.Generator().manual_seed(experts * 100 + rows)
     W = 64
     part = RoutedFFN(W, experts, top, ff, activation="silu", router_bias=False, gated=True, router="softmax_all", prefix="m",
