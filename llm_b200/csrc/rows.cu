@@ -439,6 +439,99 @@ add_layernorm_kernel(float* __restrict__ resid, MaybePartial<T> delta, const flo
     out[base + c] = from_f32<T>((row_s[c] - mean) * rstd * pre[c]);
 }
 
+// The same for rows of up to NV * 2048 elements on the 8-grid: the row stays in registers (NV vectors of eight per
+// thread), every access is 16 bytes wide, and the statistics are the same two passes (mean, then squared deviations).
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+add_layernorm_vec_kernel(float* __restrict__ resid, MaybePartial<T> delta, const float* __restrict__ post, float mult,
+                         const float* __restrict__ pre, T* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  const float inv_n = 1.f / (float)hidden;
+  float r[NV][8];
+  if (delta.present()) {
+    float y[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 256 + threadIdx.x) * 8;
+      if (c < hidden) {
+        delta.at8(base + c, y[v]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += y[v][i];
+      }
+    }
+    float mean = 0.f, rstd = 1.f;
+    if (post) {
+      mean = block_sum(s, scratch) * inv_n;
+      float q = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        if ((v * 256 + threadIdx.x) * 8 < hidden) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { const float d = y[v][i] - mean; q += d * d; }
+        }
+      }
+      rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+    }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 256 + threadIdx.x) * 8;
+      if (c < hidden) {
+        Vec8<float>::load(resid + base + c, r[v]);
+        if (post) {
+          float w[8];
+          Vec8<float>::load(post + c, w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) r[v][i] = fmaf(mult, (y[v][i] - mean) * rstd * w[i], r[v][i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) r[v][i] = fmaf(mult, y[v][i], r[v][i]);
+        }
+        Vec8<float>::store(resid + base + c, r[v]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 256 + threadIdx.x) * 8;
+      if (c < hidden) Vec8<float>::load(resid + base + c, r[v]);
+    }
+  }
+  if (!out) return;
+  float s = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if ((v * 256 + threadIdx.x) * 8 < hidden) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += r[v][i];
+    }
+  }
+  const float mean = block_sum(s, scratch) * inv_n;
+  float q = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if ((v * 256 + threadIdx.x) * 8 < hidden) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float d = r[v][i] - mean; q += d * d; }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(q, scratch) * inv_n + eps);
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = (v * 256 + threadIdx.x) * 8;
+    if (c < hidden) {
+      float w[8], o[8];
+      Vec8<float>::load(pre + c, w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (r[v][i] - mean) * rstd * w[i];
+      Vec8<T>::store(out + base + c, o);
+    }
+  }
+}
+
 // delta: [rows, hidden] of the element kind, or float32 partial results, or neither; post, pre: float32
 // [hidden] or null; out: [rows, hidden] of the element kind or null (then pre is not read).
 LLMK_API int llmk_add_layernorm(float* resid, const void* delta, const float* partials, int splits, long long split_stride,
@@ -452,9 +545,19 @@ LLMK_API int llmk_add_layernorm(float* resid, const void* delta, const float* pa
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> d{(const T*)delta, partials, splits, split_stride};
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_kernel(add_layernorm_kernel<T>, dim3(rows), dim3(256), smem, stream, resid, d, post, mult, pre, (T*)out, hidden, eps);
+    const bool vec = hidden % 8 == 0 && hidden <= 8192 && d.vector_ok() && (uintptr_t)resid % 16 == 0 && (uintptr_t)post % 16 == 0 &&
+                     (uintptr_t)pre % 16 == 0 && (uintptr_t)out % 16 == 0;
+    if (vec && hidden <= 2048)
+      launch_kernel(add_layernorm_vec_kernel<T, 1>, dim3(rows), dim3(256), 0, stream, resid, d, post, mult, pre, (T*)out, hidden, eps);
+    else if (vec && hidden <= 4096)
+      launch_kernel(add_layernorm_vec_kernel<T, 2>, dim3(rows), dim3(256), 0, stream, resid, d, post, mult, pre, (T*)out, hidden, eps);
+    else if (vec)
+      launch_kernel(add_layernorm_vec_kernel<T, 4>, dim3(rows), dim3(256), 0, stream, resid, d, post, mult, pre, (T*)out, hidden, eps);
+    else {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      launch_kernel(add_layernorm_kernel<T>, dim3(rows), dim3(256), smem, stream, resid, d, post, mult, pre, (T*)out, hidden, eps);
+    }
     LLMK_LAUNCH_CHECK("add_layernorm");
   });
 }

@@ -47,7 +47,7 @@ def i32(xs):
 
 # ---- each mechanism alone ---------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("rows,width", [(1, 8), (7, 100), (33, 256), (3, 2050)])
+@pytest.mark.parametrize("rows,width", [(1, 8), (7, 100), (33, 256), (3, 2050), (5, 4096), (3, 6152), (2, 8200)])
 def test_layernorm_on_both_sides_of_the_sum(dtype, rows, width):
     from llm_b200.csrc import ops
     g = torch.Generator().manual_seed(rows * 1000 + width)
