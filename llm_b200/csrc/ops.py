@@ -700,9 +700,11 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
         max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
         if window:
             max_keys = min(max_keys, window + keep_first)
+        # twice the ranges that the tensor-core decode kernel gets: a round of this kernel (32 keys) takes longer than a
+        # tile of that one.  Measured at head size 128, 584 keys: batch 8, 43 -> 32 us a launch; batch 64, a step 2.16 -> 1.70 ms
+        splits = max(1, min(16, 2 * decode_splits(ctx.n_entries, n_kv, max_keys), _ceil_div(max_keys, 32)))
         paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
-                               n_heads, n_kv, head_dim, window, scale,
-                               splits=decode_splits(ctx.n_entries, n_kv, max_keys), max_keys=max_keys,
+                               n_heads, n_kv, head_dim, window, scale, splits=splits, max_keys=max_keys,
                                softcap=softcap, sink=sink, keep_first=keep_first)
         return
     if (extended and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
