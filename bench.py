@@ -404,14 +404,14 @@ def fopivik_config(width, layers, heads, kv_heads, dim, window, gla_heads, gla_d
     moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
     for i in range(layers):
         if i % 2 == 0:
-            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
-                     "mask": {"size": window, "keep_first": 4},
-                     "rot": {"dims": dim // 2, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 40.0,
+                     "mask": {"size": window, "keep_first": 8},
+                     "rot": {"dims": dim // 2, "base": 5e5, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 8192}}}
             ls.append({"type": "attention", "mixer": mixer, "mlp": moe})
         else:
             ls.append({"type": "gla", "mixer": {"heads": gla_heads, "dim": gla_dim, "vdim": gla_vdim, "tau": 16.0}, "mlp": moe})
-    return {"architecture": "Fopivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
-            "logit_softcap": 30.0, "layers": ls, "loop": {"start": 0, "stop": 2, "times": 2}, "max_position": 4096}
+    return {"architecture": "Fopivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "residual_mult": 0.25,
+            "logit_softcap": 50.0, "layers": ls, "loop": {"start": 0, "stop": 2, "times": 2}, "max_position": 4096}
 
 
 # name -> (Fopivik config, Llama config of the same width and heads; Llama's depth equals Fopivik's layer runs, and its

@@ -15,7 +15,7 @@ import math
 import torch
 
 
-def attn(heads, kv_heads, dim, vdim, size, keep, rot_dims, scale, softcap=20.0, base=10000.0, scaling=None):
+def attn(heads, kv_heads, dim, vdim, size, keep, rot_dims, scale, softcap=24.0, base=10000.0, scaling=None):
     rot = {"dims": rot_dims, "base": base}
     if scaling:
         rot["scaling"] = scaling
@@ -59,7 +59,7 @@ CONFIG_B = config(128, 333, [
     layer(attn(8, 2, 64, 64, size=33, keep=20, rot_dims=32, scale=0.12, base=500000.0, scaling=SCALING), moe(6, 4, 40)),
     layer(attn(4, 4, 32, 64, size=100, keep=1, rot_dims=0, scale=0.2), moe(2, 1, 128)),
     layer(gla(2, 64, 128, tau=4.0), None),
-], loop=(1, 3, 3), eps=1e-6, mult=0.3, cap=30.0)
+], loop=(1, 3, 3), eps=1e-6, mult=0.35, cap=28.0)
 # C: nothing on a grid of 8 (width, head sizes, feed-forward sizes); a loop over everything, once
 CONFIG_C = config(100, 97, [
     layer(attn(3, 1, 10, 6, size=7, keep=2, rot_dims=6, scale=0.35), moe(5, 2, 14)),
@@ -73,9 +73,9 @@ CONFIG_D = config(64, 120, [layer(attn(2, 1, 32, 16, size=24, keep=4, rot_dims=8
 CONFIG_E = config(48, 150, [layer(gla(2, 24, 16, tau=32.0), None)], loop=(0, 1, 4), mult=0.7, cap=35.0)
 # F: attention that decodes on the tensor-core kernels' sizes, window wider than any request here
 CONFIG_F = config(128, 256, [
-    layer(attn(8, 1, 64, 64, size=4096, keep=4, rot_dims=16, scale=0.11, base=1e6, scaling=SCALING), moe(4, 2, 64)),
+    layer(attn(6, 2, 64, 64, size=4096, keep=5, rot_dims=24, scale=0.11, base=5e5, scaling=SCALING), moe(4, 2, 64)),
     layer(attn(4, 2, 128, 128, size=50, keep=0, rot_dims=128, scale=0.08), moe(4, 2, 64)),
-], loop=(1, 2, 2), mult=0.3)
+], loop=(1, 2, 2), mult=0.45)
 
 CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 16), "C": (CONFIG_C, 8), "D": (CONFIG_D, 16), "E": (CONFIG_E, 32),
            "F": (CONFIG_F, 16)}   # name -> (config, page size)

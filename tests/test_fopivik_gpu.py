@@ -163,7 +163,7 @@ ATTN_CASES = [  # H, G, D, V, window, keep_first, softcap, sink, T
     (5, 5, 8, 24, 0, 0, 15.0, False, 50),
     (2, 1, 32, 32, 1, 1, 30.0, True, 20),
     (1, 1, 24, 40, 16, 40, 10.0, False, 90),
-    (8, 1, 64, 64, 40, 4, 20.0, True, 130),
+    (6, 1, 64, 64, 40, 5, 18.0, True, 130),
 ]
 
 
