@@ -162,6 +162,146 @@ gla_scan_kernel(float* __restrict__ out, long long out_stride, const T* __restri
   }
 }
 
+// ---- the two passes of a segmented run, with the next chunk in flight -------------------------------------
+// Same work split and arithmetic as gla_scan_kernel in modes 1 and 2, but a chunk's q, k, decays and v are brought
+// into shared memory as they lie in global memory by asynchronous 16-byte copies (cp.async), two stages deep, so that
+// the copies of chunk i + 1 run under the multiply-adds of chunk i; the values are widened to float32 when they are
+// read from shared memory, and q's scale is applied to the output sums.  Needs rows on the 16-byte grid (dim a
+// multiple of 8, vdim a multiple of the tile) and the decays made beforehand (gla_decay_kernel).
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 f = *reinterpret_cast<const float4*>(p);
+  v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  v[0] = __low2float(h[0]); v[1] = __high2float(h[0]); v[2] = __low2float(h[1]); v[3] = __high2float(h[1]);
+}
+
+template <typename T, int VT>
+__global__ void __launch_bounds__(VT / COLS * MAX_GROUPS)
+gla_scan_pipe_kernel(float* __restrict__ out, long long out_stride, const T* __restrict__ q, const T* __restrict__ k,
+                     const T* __restrict__ v, long long qkv_stride, const float* __restrict__ a, long long a_stride,
+                     float q_scale, const int* __restrict__ cu_tokens, int heads, int dim, int vdim, int seg_len,
+                     int max_segs, int mode, float* __restrict__ seg_state, float* __restrict__ seg_decay) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int TX = VT / COLS;
+  const int groups = blockDim.y;                       // dim == groups * ROWS here
+  const size_t qk_bytes = (size_t)CHUNK * dim * sizeof(T), a_bytes = (size_t)CHUNK * dim * sizeof(float);
+  const size_t v_bytes = (size_t)CHUNK * VT * sizeof(T), stage_bytes = 2 * qk_bytes + a_bytes + v_bytes;
+  float* part = reinterpret_cast<float*>(smem_raw + 2 * stage_bytes);      // [CHUNK][groups][VT]
+  const int j = threadIdx.x, g = threadIdx.y;
+  const int tid = g * TX + j, nthreads = TX * groups;
+  const int entry = blockIdx.z / max_segs, seg = blockIdx.z % max_segs, head = blockIdx.y;
+  const int col0 = blockIdx.x * VT + j * COLS;
+  int t0 = cu_tokens[entry], t1 = cu_tokens[entry + 1];
+  if (seg * seg_len >= t1 - t0) return;
+  size_t seg_index = seg;
+  for (int e = 0; e < entry; ++e) seg_index += (cu_tokens[e + 1] - cu_tokens[e] + seg_len - 1) / seg_len;
+  t0 += seg * seg_len;
+  t1 = min(t1, t0 + seg_len);
+  float* S_g = seg_state + ((seg_index * heads + head) * dim) * vdim;
+
+  auto issue = [&](int c0, int stage) {
+    const int n = min(CHUNK, t1 - c0);
+    unsigned char* base = smem_raw + stage * stage_bytes;
+    const int rv = dim * (int)sizeof(T) / 16, av = dim * 4 / 16, vv = VT * (int)sizeof(T) / 16;
+    for (int idx = tid; idx < n * rv; idx += nthreads) {
+      const int c = idx / rv, x = idx % rv;
+      const size_t src = (size_t)(c0 + c) * qkv_stride + (size_t)head * dim;
+      if (mode != 1) cp_async16(base + (size_t)c * dim * sizeof(T) + x * 16, reinterpret_cast<const char*>(q + src) + x * 16);
+      cp_async16(base + qk_bytes + (size_t)c * dim * sizeof(T) + x * 16, reinterpret_cast<const char*>(k + src) + x * 16);
+    }
+    for (int idx = tid; idx < n * av; idx += nthreads) {
+      const int c = idx / av, x = idx % av;
+      cp_async16(base + 2 * qk_bytes + (size_t)c * dim * 4 + x * 16,
+                 reinterpret_cast<const char*>(a + (size_t)(c0 + c) * a_stride + (size_t)head * dim) + x * 16);
+    }
+    for (int idx = tid; idx < n * vv; idx += nthreads) {
+      const int c = idx / vv, x = idx % vv;
+      cp_async16(base + 2 * qk_bytes + a_bytes + (size_t)c * VT * sizeof(T) + x * 16,
+                 reinterpret_cast<const char*>(v + (size_t)(c0 + c) * qkv_stride + (size_t)head * vdim + blockIdx.x * VT) + x * 16);
+    }
+  };
+
+  float S[ROWS][COLS], A[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) S[r][c] = mode == 2 ? S_g[(size_t)(g * ROWS + r) * vdim + col0 + c] : 0.f;
+    A[r] = 1.f;
+  }
+  issue(t0, 0);
+  cp_async_commit();
+  int stage = 0;
+  for (int c0 = t0; c0 < t1; c0 += CHUNK, stage ^= 1) {
+    const int n = min(CHUNK, t1 - c0);
+    if (c0 + CHUNK < t1) issue(c0 + CHUNK, stage ^ 1);     // the other stage was read two iterations ago (barrier below)
+    cp_async_commit();
+    cp_async_wait<1>();                                    // this chunk's copies have landed (the newest group may fly)
+    __syncthreads();
+    const unsigned char* base = smem_raw + stage * stage_bytes;
+    const T* q_s = reinterpret_cast<const T*>(base);
+    const T* k_s = reinterpret_cast<const T*>(base + qk_bytes);
+    const float* a_s = reinterpret_cast<const float*>(base + 2 * qk_bytes);
+    const T* v_s = reinterpret_cast<const T*>(base + 2 * qk_bytes + a_bytes);
+    for (int c = 0; c < n; ++c) {
+      float vv[COLS], kc[ROWS], ac[ROWS], qc[ROWS];
+      load4<T>(v_s + c * VT + j * COLS, vv);
+      Vec8<T>::load(k_s + c * dim + g * ROWS, kc);
+      Vec8<float>::load(a_s + c * dim + g * ROWS, ac);
+      if (mode == 1) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+          for (int cc = 0; cc < COLS; ++cc) S[r][cc] = fmaf(ac[r], S[r][cc], kc[r] * vv[cc]);
+          A[r] *= ac[r];
+        }
+        continue;
+      }
+      Vec8<T>::load(q_s + c * dim + g * ROWS, qc);
+      float o[COLS] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+        for (int cc = 0; cc < COLS; ++cc) {
+          S[r][cc] = fmaf(ac[r], S[r][cc], kc[r] * vv[cc]);
+          o[cc] = fmaf(S[r][cc], qc[r], o[cc]);
+        }
+      }
+      *reinterpret_cast<float4*>(part + (c * groups + g) * VT + j * COLS) = make_float4(o[0], o[1], o[2], o[3]);
+    }
+    __syncthreads();                                       // the stage is free for the copies after next; part is complete
+    if (mode == 1) continue;
+    for (int idx = tid; idx < n * VT; idx += nthreads) {
+      const int c = idx / VT, jj = idx % VT;
+      float o = 0.f;
+      for (int gg = 0; gg < groups; ++gg) o += part[(c * groups + gg) * VT + jj];
+      out[(size_t)(c0 + c) * out_stride + (size_t)head * vdim + blockIdx.x * VT + jj] = o * q_scale;
+    }
+    // part is read here and written again only after the next iteration's first barrier
+  }
+  cp_async_wait<0>();
+  if (mode == 2) return;
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int d = g * ROWS + r;
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) S_g[(size_t)d * vdim + col0 + c] = S[r][c];
+    if (blockIdx.x == 0 && j == 0) seg_decay[(seg_index * heads + head) * dim + d] = A[r];
+  }
+}
+
 // z <- sigmoid(z + bias)^(1 / tau) in place: the decays of a step, made once where several CTAs and two passes read them.
 __global__ void gla_decay_kernel(float* __restrict__ z, long long z_stride, const float* __restrict__ z_bias, float inv_tau,
                                  int cols, size_t total) {
@@ -240,7 +380,24 @@ LLMK_API int llmk_gla_scan(float* out, long long out_stride, const void* q, cons
                            state, state_slots, cu_tokens, heads, dim, vdim, seg_len, max_segs, mode, seg_state, seg_decay,
                            seg_len ? 1 : 0);
     };
+    // the passes of a segmented run take the kernel with asynchronous copies where every row lies on the 16-byte grid
+    const bool pipe = seg_len > 0 && dim % 8 == 0 && vdim % vt == 0 && qkv_stride % 8 == 0 && z_stride % 4 == 0 &&
+                      (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 && (uintptr_t)v % 16 == 0 && (uintptr_t)z % 16 == 0;
+    auto launch_pipe = [&](auto kern, int VT, int mode) {
+      const size_t stage = 2 * (size_t)CHUNK * dim * sizeof(T) + (size_t)CHUNK * dim * sizeof(float) + (size_t)CHUNK * VT * sizeof(T);
+      const size_t smem = 2 * stage + sizeof(float) * (size_t)CHUNK * groups * VT;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      return launch_kernel(kern, dim3(vdim / VT, heads, n_entries * max_segs), dim3(VT / COLS, groups), smem, stream, out, out_stride,
+                           (const T*)q, (const T*)k, (const T*)v, qkv_stride, (const float*)z, z_stride, q_scale, cu_tokens, heads, dim,
+                           vdim, seg_len, max_segs, mode, seg_state, seg_decay);
+    };
     auto pass = [&](int mode) {
+      if (pipe) {
+        if (vt == 32) launch_pipe(gla_scan_pipe_kernel<T, 32>, 32, mode);
+        else if (vt == 16) launch_pipe(gla_scan_pipe_kernel<T, 16>, 16, mode);
+        else launch_pipe(gla_scan_pipe_kernel<T, 8>, 8, mode);
+        return;
+      }
       if (vt == 32) launch(gla_scan_kernel<T, 32>, 32, mode);
       else if (vt == 16) launch(gla_scan_kernel<T, 16>, 16, mode);
       else launch(gla_scan_kernel<T, 8>, 8, mode);

@@ -320,15 +320,18 @@ def test_prompt_attention_on_the_tensor_cores_with_the_options(case):
     assert max_err(out[1:T + 1].view(T, H, D), want) < 1e-2
 
 
-@pytest.mark.parametrize("H,D,V,tau", [(2, 16, 24, 8.0), (1, 130, 33, 1.0), (3, 64, 40, 32.0)])
-def test_gla_segments_side_by_side_equal_the_single_pass(H, D, V, tau):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,D,V,tau", [(2, 16, 24, 8.0), (1, 130, 33, 1.0), (3, 64, 40, 32.0), (2, 16, 32, 8.0), (4, 64, 64, 16.0), (1, 128, 256, 4.0),
+                                       (3, 8, 8, 2.0)])
+def test_gla_segments_side_by_side_equal_the_single_pass(H, D, V, tau, dtype):
     from llm_b200.csrc import ops
     g = torch.Generator().manual_seed(H + D)
     lens = [150, 1, 64, 65, 7]
     T, cu = sum(lens), [0]
     for n in lens:
         cu.append(cu[-1] + n)
-    x = dev(bf(torch.randn(T, 2 * H * D + H * V, generator=g) * 0.7))
+    # rows on the 16-byte grid take the passes with asynchronous copies, the others the plain passes
+    x = dev(bf(torch.randn(T, 2 * H * D + H * V, generator=g) * 0.7), dtype)
     z, b = dev(torch.randn(T, H * D, generator=g) * 2 + 2), dev(torch.randn(H * D, generator=g))
     q, k, v = x[:, :H * D], x[:, H * D:2 * H * D], x[:, 2 * H * D:]
     start = torch.randn(6, H, D, V, generator=g).cuda()                 # the requests come with a past
